@@ -6,8 +6,13 @@
 // which is the lower-right aligned causal mask for a portion of a prompt on top of cached
 // tokens, and a single decoded token alike.  Online softmax (running max m, running sum l)
 // over tiles of 128 keys.  Keys have D dimensions and values Dv (the pools have their own widths).
-// With `sink` the softmax has one more, imaginary key of score 0 and no value: the weights are
-// exp(s_j) / (1 + sum exp(s_j)); the running pair starts at (m, l) = (0, 1) instead of (-inf, 0).  Any head_dim that is a multiple of 4 (float) / 8 (bfloat16) up to
+// With `mask_mode` 1 the number `window` is a chunk size instead: position p sees the keys of its own
+// chunk, floor(p / size) * size <= b <= p (chunks counted from position 0 of the sequence).
+// With `sink` the softmax has one more, imaginary key and no value for it: the weights are
+// exp(s_j) / (exp(z) + sum exp(s_j)), z = sink_values[head] (unscaled), or 0 without `sink_values`;
+// the running pair starts at (m, l) = (z, 1) instead of (-inf, 0).
+// With `turn_freq` (float [Dv/2]) the result of every head is turned back: pair (m, m + Dv/2) by
+// -p * turn_freq[m] (the values were stored turned by their own positions).  Any head_dim that is a multiple of 4 (float) / 8 (bfloat16) up to
 // 512, any G.  This kernel is the attention of the 32-bit path and the fallback of the
 // bfloat16 path for head sizes the tensor-core kernel is not built for.
 //
@@ -27,12 +32,14 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
                     const T* __restrict__ v_pool, const int* __restrict__ page_table,
                     int pt_stride, const int* __restrict__ positions,
                     const int* __restrict__ seq_of_token, T* __restrict__ out, long out_stride,
-                    int H, int KVH, int D, int Dv, int page_size, int num_pages, int window, float scale,
-                    int sink, int* err) {
+                    int H, int KVH, int D, int Dv, int page_size, int num_pages, int window, int mask_mode,
+                    float scale, int sink, const float* __restrict__ sink_values,
+                    const float* __restrict__ turn_freq, int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                       // [GCHUNK][D]
   float* ps = qs + GCHUNK * D;            // [GCHUNK][THREADS]
   long* slot = (long*)(ps + GCHUNK * THREADS);  // [THREADS] row of each key in the pools (-1: none)
+  float* os = (float*)(slot + THREADS);   // [GCHUNK][Dv] results before they are turned back (with turn_freq)
   __shared__ float red[GCHUNK][THREADS / 32];
 
   const int t = blockIdx.x, kvh = blockIdx.y;
@@ -41,7 +48,7 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
   if (pos < 0) return;
   const int seq = seq_of_token[t];
   const int G = H / KVH;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = window > 0 ? (mask_mode == 1 ? (pos / window) * window : max(0, pos - window + 1)) : 0;
   const int hi = pos;
   const int* table = page_table + (size_t)seq * pt_stride;
 
@@ -55,7 +62,7 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
     float m[GCHUNK], l[GCHUNK], acc[GCHUNK][DPT];
 #pragma unroll
     for (int g = 0; g < GCHUNK; ++g) {
-      m[g] = sink ? 0.f : -INFINITY;
+      m[g] = sink ? ((sink_values && g < gn) ? sink_values[kvh * G + g0 + g] : 0.f) : -INFINITY;
       l[g] = sink ? 1.f : 0.f;
 #pragma unroll
       for (int j = 0; j < DPT; ++j) acc[g][j] = 0.f;
@@ -149,9 +156,25 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
 #pragma unroll
       for (int dd = 0; dd < DPT; ++dd) {
         const int d = tid + dd * THREADS;
-        if (d < Dv)
+        if (d >= Dv) continue;
+        if (turn_freq)
+          os[g * Dv + d] = acc[g][dd] * inv;
+        else
           out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d] =
               from_f32<T>(acc[g][dd] * inv);
+      }
+    }
+    if (turn_freq) {
+      __syncthreads();
+      const int half = Dv / 2;
+      for (int i = tid; i < gn * Dv; i += THREADS) {
+        const int g = i / Dv, d = i % Dv;
+        const int mth = d < half ? d : d - half;
+        float sn, cn;
+        sincosf((float)pos * turn_freq[mth], &sn, &cn);
+        // the inverse turn: (u, v) -> (u cos + v sin, v cos - u sin)
+        const float v = d < half ? os[i] * cn + os[i + half] * sn : os[i] * cn - os[i - half] * sn;
+        out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d] = from_f32<T>(v);
       }
     }
   }
@@ -162,7 +185,8 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
                                 const void* v_pool, const int* page_table, int pt_stride,
                                 const int* positions, const int* seq_of_token, void* out,
                                 long out_stride, int T, int H, int KVH, int D, int Dv, int page_size,
-                                int num_pages, int window, float scale, int sink, int dtype,
+                                int num_pages, int window, int mask_mode, float scale, int sink,
+                                const float* sink_values, const float* turn_freq, int dtype,
                                 cudaStream_t stream) {
   if (T == 0) return 0;
   DSP_REQUIRE(KVH > 0 && H % KVH == 0, "dsp_attn_generic: H=%d is not a multiple of KVH=%d", H, KVH);
@@ -170,9 +194,12 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
               "dsp_attn_generic: key size %d or value size %d outside the kernel's range (values up to %d)", D, Dv,
               THREADS * DPT);
   DSP_REQUIRE(KVH <= 65535, "dsp_attn_generic: too many KV heads");
+  DSP_REQUIRE(mask_mode == 0 || mask_mode == 1, "dsp_attn_generic: unknown mask mode %d", mask_mode);
+  DSP_REQUIRE(!turn_freq || Dv % 2 == 0, "dsp_attn_generic: values of an odd width %d cannot be turned", Dv);
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_attn_generic: no device error word");
-  const size_t smem = (size_t)(GCHUNK * D + GCHUNK * THREADS) * sizeof(float) + THREADS * sizeof(long);
+  const size_t smem = (size_t)(GCHUNK * D + GCHUNK * THREADS + (turn_freq ? GCHUNK * Dv : 0)) * sizeof(float) +
+                      THREADS * sizeof(long);
   dim3 grid(T, KVH);
   if (dtype == DSP_F32) {
     static size_t configured = 0;
@@ -184,7 +211,7 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
     attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
         (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, page_table, pt_stride,
         positions, seq_of_token, (float*)out, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
-        scale, sink, err);
+        mask_mode, scale, sink, sink_values, turn_freq, err);
   } else if (dtype == DSP_BF16) {
     static size_t configured = 0;
     if (smem > configured) {
@@ -195,7 +222,7 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
     attn_generic_kernel<bf16><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride,
         positions, seq_of_token, (bf16*)out, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
-        scale, sink, err);
+        mask_mode, scale, sink, sink_values, turn_freq, err);
   } else {
     DSP_REQUIRE(false, "dsp_attn_generic: unknown dtype %d", dtype);
   }

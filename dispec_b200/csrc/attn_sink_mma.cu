@@ -1,21 +1,25 @@
 // Tensor-core attention (mma.sync m16n8k16, bfloat16 operands, 32-bit scores, softmax and sums)
-// over paged keys of width DSP_DK and values of width DSP_DV, with a sliding window and an
-// optional sink in the softmax (one more key of score 0 and no value: the running pair of the
-// online softmax starts at (max, sum) = (0, 1) instead of (-inf, 0)).  Compiled per pair of widths.
+// over paged keys of width DSP_DK and values of width DSP_DV, with a sliding window or a chunked
+// mask and an optional sink in the softmax (one more key with no value, of score 0 or, with
+// `sink_values`, of the head's own unscaled score z: the running pair of the online softmax starts
+// at (max, sum) = (z, 1) instead of (-inf, 0)).  With `turn_freq` every head's result is turned
+// back, pair (m, m + DV/2) by -p * turn_freq[m] (values that were stored turned by their own
+// positions).  Compiled per pair of widths.
 //
 // A block of four warps takes one tile of the step's tile list and one key/value head: up to 64
 // query rows = (token, head of the group) pairs of one request, 16 rows a warp.  Keys come in
 // tiles of 64 from the first key any row of the tile may see, two tiles in flight (cp.async);
 // a key row is found through the request's page table, a page id outside the pool is recorded
 // and its keys are hidden from every row.  The query at position p sees keys j with
-// p - window < j <= p (window 0: every j <= p); positions follow from the request's stored length
+// p - window < j <= p (window 0: every j <= p; mask_mode 1: the keys of p's own chunk of `window`
+// positions, floor(p / window) * window <= j <= p); positions follow from the request's stored length
 // (ctx_len) and the number of tokens it brings.  A request of length 0 (a padding row of a
 // captured step) is skipped.
 //
 // Key splits (single tokens, whose one tile would otherwise walk its window alone): with
 // splits > 1 the grid's z index takes a share of the tile's key tiles and leaves an unnormalised
 // output with its (max, sum) in the scratch that attn_combine.cu merges; only split 0 starts from
-// the sink's (0, 1), so the sink is counted once.
+// the sink's (z, 1), so the sink is counted once; the merged result is turned back there.
 #include "common.cuh"
 
 #ifndef DSP_DK
@@ -56,9 +60,10 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
                      const bf16* __restrict__ v_pool, const int* __restrict__ page_table, int pt_stride,
                      const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                      const int* __restrict__ tile_seq, const int* __restrict__ tile_tok0, bf16* __restrict__ out,
-                     long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, float scale_log2,
-                     int sink, int tile_offset, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                     int* err) {
+                     long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, int mask_mode,
+                     float scale_log2, int sink, const float* __restrict__ sink_values,
+                     const float* __restrict__ turn_freq, int tile_offset, int splits,
+                     float* __restrict__ part_o, float* __restrict__ part_ml, int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [BM][LDK]
   bf16* Ks = Qs + BM * LDK;                      // [2][BN][LDK]
@@ -70,7 +75,11 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
   const int group = H / G;
   const int nt = min(tpt, qlen - tok0), rows = nt * group;
   const int pos0 = clen - qlen + tok0, p1 = pos0 + nt - 1;
-  const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  // the first key a row at position p sees
+  auto first_seen = [&](int p) {
+    return window > 0 ? (mask_mode == 1 ? (p / window) * window : max(0, p - window + 1)) : 0;
+  };
+  const int lo = first_seen(pos0);
   const int nkt_all = (p1 - lo) / BN + 1;
   const int kt0 = (int)((long)nkt_all * split / splits), kt1 = (int)((long)nkt_all * (split + 1) / splits);
   const int nkt = kt1 - kt0;  // this block's key tiles: kt0 .. kt1 - 1 (none: it leaves an empty partial)
@@ -127,9 +136,14 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
 
   const int ra = warp * 16 + (lane >> 2), rb = ra + 8;  // the two rows of this thread's fragments
   const int pa = ra < rows ? pos0 + ra / group : -1, pb = rb < rows ? pos0 + rb / group : -1;
+  const int la = first_seen(max(pa, 0)), lb = first_seen(max(pb, 0));
   float m[2], l[2], o[DV / 8][4];
   const bool with_sink = sink && split == 0;
   m[0] = m[1] = with_sink ? 0.f : -INFINITY;
+  if (with_sink && sink_values) {  // the head's own score, in the base-2 domain of the scores
+    if (ra < rows) m[0] = sink_values[g * group + ra % group] * 1.4426950408889634f;
+    if (rb < rows) m[1] = sink_values[g * group + rb % group] * 1.4426950408889634f;
+  }
   l[0] = l[1] = (with_sink && (lane & 3) == 0) ? 1.f : 0.f;
 #pragma unroll
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -167,7 +181,7 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
       for (int e = 0; e < 4; ++e) {
         const int j = j0 + i * 8 + (lane & 3) * 2 + (e & 1);
         const int p = e < 2 ? pa : pb;
-        const bool seen = !hide_all && j <= p && (window <= 0 || j > p - window);
+        const bool seen = !hide_all && j <= p && j >= (e < 2 ? la : lb);
         s[i][e] = seen ? s[i][e] * scale_log2 : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
       }
@@ -231,6 +245,19 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
       continue;
     }
     const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+    if (turn_freq) {  // pair (d, d + DV/2) is held by this thread: o[i] and o[i + DV/16]
+      const float p = (float)(h == 0 ? pa : pb);
+#pragma unroll
+      for (int i = 0; i < DV / 16; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float sn, cn;
+          sincosf(p * turn_freq[i * 8 + (lane & 3) * 2 + e], &sn, &cn);
+          const float u = o[i][2 * h + e], v = o[i + DV / 16][2 * h + e];
+          o[i][2 * h + e] = u * cn + v * sn;  // the inverse turn
+          o[i + DV / 16][2 * h + e] = v * cn - u * sn;
+        }
+    }
     bf16* dst = out + token * ldo + (size_t)head * DV + (lane & 3) * 2;
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i)
@@ -246,10 +273,12 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
 extern "C" int DSP_CAT(dsp_attn_sink_mma_k, DSP_DK, _v, DSP_DV)(
     const void* q, long ldq, const void* k_pool, const void* v_pool, const int* page_table, int pt_stride,
     const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0, int tile_offset, int num_tiles,
-    void* out, long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, float scale, int sink,
-    int splits, float* part_o, float* part_ml, int* err, cudaStream_t stream) {
+    void* out, long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, int mask_mode, float scale,
+    int sink, const float* sink_values, const float* turn_freq, int splits, float* part_o, float* part_ml, int* err,
+    cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   if (G <= 0 || H % G || tpt <= 0 || tpt * (H / G) > BM || G > 65535 || page_size <= 0 || !err) return 2;
+  if (mask_mode < 0 || mask_mode > 1) return 2;
   if (splits < 1 || splits > 32 || (splits > 1 && (!part_o || !part_ml))) return 2;
   if (((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) || ((uintptr_t)v_pool % 16) || ((uintptr_t)out % 4) || ldq % 8 || ldo % 2)
     return 3;
@@ -263,6 +292,7 @@ extern "C" int DSP_CAT(dsp_attn_sink_mma_k, DSP_DK, _v, DSP_DV)(
   const cudaError_t e = launch_plain(attn_sink_mma_kernel, dim3(num_tiles, G, splits), dim3(128), smem, stream, (const bf16*)q, ldq,
                                      (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride, q_start, ctx_len,
                                      tile_seq, tile_tok0, (bf16*)out, ldo, H, G, tpt, page_size, num_pages, window,
-                                     scale * 1.4426950408889634f, sink, tile_offset, splits, part_o, part_ml, err);
+                                     mask_mode, scale * 1.4426950408889634f, sink, sink_values, turn_freq, tile_offset,
+                                     splits, part_o, part_ml, err);
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

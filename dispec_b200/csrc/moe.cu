@@ -3,7 +3,7 @@
 // tiles and blocks beyond the real number leave at once, so a step can be captured in a graph).
 //
 //   dsp_moe_route    scores = softmax(W_router h) over all experts in 32-bit (W_router float, h of
-//                    either type); experts form `groups` equal runs of neighbours, a group's score
+//                    either type), or with `score_kind` 1 the sigmoid of every logit; experts form `groups` equal runs of neighbours, a group's score
 //                    is its largest score, only experts of the `keep` best groups can be chosen;
 //                    the `top` largest of those are the token's experts, their scores its weights
 //                    (not renormalised).  Equal scores: the lower index wins.  One block per token.
@@ -11,11 +11,18 @@
 //                    and cuts every expert's run into tiles of TILE_ROWS rows.  One block.
 //   dsp_moe_product  C[c_row(i)] = act(A[a_row(i)] B_e^T) for the sorted pairs i of every expert e
 //                    (B: [experts, N, K]); a_row / c_row are optional index lists (gather, scatter).
-//                    act 0: none, 1: the square of relu.  Every output is one chain of fused
+//                    act 0: none, 1: the square of relu, 2: a clamped gated unit over neighbouring
+//                    columns: column 2j is the gate and 2j + 1 the up value of output j (B holds the
+//                    two matrices' rows in turn), both times row_scale[pair] when that is given (a
+//                    factor on the pair's input row, applied to the 32-bit sums, which is the same
+//                    product), g = min(gate, limit), u = clamp(up, -limit, limit),
+//                    C[., j] = g * sigmoid(alpha * g) * (u + 1); C is N / 2 wide.
+//                    Every output is one chain of fused
 //                    multiply-adds in ascending k, so a pair's result depends on nothing but its own
 //                    row and its expert.  With `tensor_cores` (bfloat16 operands): mma.sync tiles of
 //                    64 pairs (1) or 128 pairs (2); the plan must have been made for tiles of that many rows.
-//   dsp_moe_combine  y[t] = sum_k weight[t, k] * P[t * top + k], in ascending k.
+//   dsp_moe_combine  y[t] = base[t] + sum_k weight[t, k] * P[t * top + k], in ascending k (without
+//                    `base`: from 0; without `weight`: every weight 1).
 #include "common.cuh"
 
 namespace {
@@ -25,6 +32,11 @@ constexpr int TILE_ROWS = 32, TILE_COLS = 64, TILE_K = 32;
 constexpr int MMA_ROWS = 64, MMA_ROWS_WIDE = 128, MMA_COLS = 128, MMA_K = 64, MMA_PAD = 8;
 constexpr int MMA_LD = MMA_K + MMA_PAD;
 constexpr size_t mma_smem_bytes(int rows, int stages) { return sizeof(bf16) * stages * (rows + MMA_COLS) * MMA_LD; }
+
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
+}
 
 struct Best {
   float v;
@@ -47,7 +59,7 @@ __device__ __forceinline__ Best warp_best(Best b) {
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float* __restrict__ w, int T, int W, int E,
-                 int groups, int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
+                 int groups, int keep, int top, int score_kind, int* __restrict__ ids, float* __restrict__ wts) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const long t = blockIdx.x;
@@ -83,7 +95,7 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
   sum = warp_sum(sum);
   __syncwarp();
   for (int e = lane; e < E; e += 32) {
-    sc[e] = expf(sc[e] - mx) / sum;
+    sc[e] = score_kind == 1 ? 1.f / (1.f + expf(-sc[e])) : expf(sc[e] - mx) / sum;
     ok[e] = 0.f;
   }
   __syncwarp();
@@ -159,12 +171,14 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
                    const T* __restrict__ B, void* __restrict__ C, int c_dtype, long ldc,
                    const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
                    const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
-                   const int* __restrict__ n_tiles, int N, int K, int act) {
+                   const int* __restrict__ n_tiles, int N, int K, int act, const float* __restrict__ row_scale,
+                   float limit, float alpha) {
   const int tile = blockIdx.x;
   if (tile >= *n_tiles) return;
   __shared__ float As[TILE_K][TILE_ROWS + 1];
   __shared__ float Bs[TILE_K][TILE_COLS + 1];
   __shared__ long arow[TILE_ROWS], crow[TILE_ROWS];
+  __shared__ float rscale[TILE_ROWS];
   const int e = tile_expert[tile], r0 = tile_row0[tile], nr = tile_rows[tile];
   const int n0 = blockIdx.y * TILE_COLS;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -172,6 +186,7 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
     const int i = r0 + tid;
     arow[tid] = tid < nr ? (a_rows ? (long)(a_rows[i] / a_div) : (long)i) : -1;
     crow[tid] = tid < nr ? (c_rows ? (long)c_rows[i] : (long)i) : -1;
+    rscale[tid] = (tid < nr && row_scale) ? row_scale[a_rows ? a_rows[i] : i] : 1.f;
   }
   __syncthreads();
   const T* Be = B + (size_t)e * N * K;
@@ -202,6 +217,16 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
   for (int i = 0; i < 2; ++i) {
     const long cr = crow[ty * 2 + i];
     if (cr < 0) continue;
+    if (act == 2) {
+      const float f = rscale[ty * 2 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int n = n0 + tx * 4 + j;
+        if (n + 1 >= N) continue;
+        st_any(C, c_dtype, (size_t)cr * ldc + n / 2, clamped_glu(acc[i][j] * f, acc[i][j + 1] * f, limit, alpha));
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
@@ -242,7 +267,8 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
                        const bf16* __restrict__ B, void* __restrict__ C, int c_dtype, long ldc,
                        const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
                        const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
-                       const int* __restrict__ n_tiles, int N, int K, int act) {
+                       const int* __restrict__ n_tiles, int N, int K, int act, const float* __restrict__ row_scale,
+                       float limit, float alpha) {
   const int tile = blockIdx.x;
   if (tile >= *n_tiles) return;
   extern __shared__ __align__(16) unsigned char mma_smem[];
@@ -250,6 +276,7 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
   bf16 (*Bs)[MMA_COLS][MMA_LD] =
       reinterpret_cast<bf16 (*)[MMA_COLS][MMA_LD]>(mma_smem + sizeof(bf16) * STAGES * ROWS * MMA_LD);
   __shared__ long arow[ROWS], crow[ROWS];
+  __shared__ float rscale[ROWS];
   const int e = tile_expert[tile], r0 = tile_row0[tile], nr = tile_rows[tile];
   const int n0 = blockIdx.y * MMA_COLS;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -258,6 +285,7 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
     const int i = r0 + tid;
     arow[tid] = tid < nr ? (a_rows ? (long)(a_rows[i] / a_div) : (long)i) : -1;
     crow[tid] = tid < nr ? (c_rows ? (long)c_rows[i] : (long)i) : -1;
+    rscale[tid] = (tid < nr && row_scale) ? row_scale[a_rows ? a_rows[i] : i] : 1.f;
   }
   __syncthreads();
   const bf16* Be = B + (size_t)e * N * K;
@@ -319,6 +347,17 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
     for (int half = 0; half < 2; ++half) {
       const long cr = crow[wm * 32 + i * 16 + half * 8 + (lane >> 2)];
       if (cr < 0) continue;
+      if (act == 2) {  // the thread's two neighbouring columns are a gate and its up value
+        const float f = rscale[wm * 32 + i * 16 + half * 8 + (lane >> 2)];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int n = n0 + wn * 64 + j * 8 + (lane & 3) * 2;
+          if (n + 1 >= N) continue;
+          st_any(C, c_dtype, (size_t)cr * ldc + n / 2,
+                 clamped_glu(acc[i][j][half * 2] * f, acc[i][j][half * 2 + 1] * f, limit, alpha));
+        }
+        continue;
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -337,14 +376,15 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restrict__ wts, const int* __restrict__ ids,
-                   float* __restrict__ y, long ldy, long T, int top, int width) {
+                   const float* __restrict__ base, long ldb, float* __restrict__ y, long ldy, long T, int top,
+                   int width) {
   const long n = T * width;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
     const long t = i / width;
     const int c = (int)(i % width);
-    float acc = 0.f;
+    float acc = base ? base[(size_t)t * ldb + c] : 0.f;
     for (int k = 0; k < top; ++k)
-      if (ids[t * top + k] >= 0) acc = fmaf(wts[t * top + k], P[(size_t)(t * top + k) * ldp + c], acc);
+      if (ids[t * top + k] >= 0) acc = fmaf(wts ? wts[t * top + k] : 1.f, P[(size_t)(t * top + k) * ldp + c], acc);
     y[(size_t)t * ldy + c] = acc;
   }
 }
@@ -354,8 +394,9 @@ moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restric
 extern "C" int dsp_moe_tile_rows(int tensor_cores) { return tensor_cores == 2 ? MMA_ROWS_WIDE : tensor_cores ? MMA_ROWS : TILE_ROWS; }
 
 extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* w, int T, int W, int E, int groups,
-                             int keep, int top, int* ids, float* wts, cudaStream_t stream) {
+                             int keep, int top, int score_kind, int* ids, float* wts, cudaStream_t stream) {
   if (T == 0) return 0;
+  DSP_REQUIRE(score_kind == 0 || score_kind == 1, "dsp_moe_route: unknown score kind %d", score_kind);
   DSP_REQUIRE(h && w && ids && wts, "dsp_moe_route: missing operand");
   DSP_REQUIRE(E > 0 && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && top > 0 &&
                   top <= keep * (E / groups),
@@ -363,7 +404,7 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
   const size_t smem = (size_t)(2 * E + groups + W) * sizeof(float);
   DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts over a width of %d are more than the router kernel holds", E, W);
   DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)T), dim3(128), smem, stream, h, h_dtype, ldh, w, T, W, E,
-                        groups, keep, top, ids, wts));
+                        groups, keep, top, score_kind, ids, wts));
   DSP_CHECK_LAUNCH("dsp_moe_route");
   return 0;
 }
@@ -386,10 +427,13 @@ extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int rows_per_til
 extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int* a_rows, int a_div, const void* B,
                                void* C, int c_dtype, long ldc, const int* c_rows, const int* tile_expert,
                                const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles, int N,
-                               int K, int act, int tensor_cores, cudaStream_t stream) {
+                               int K, int act, const float* row_scale, float limit, float alpha, int tensor_cores,
+                               cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
   DSP_REQUIRE(A && B && C && tile_expert && tile_row0 && tile_rows && n_tiles && a_div > 0, "dsp_moe_product: missing operand");
-  DSP_REQUIRE(act == 0 || act == 1, "dsp_moe_product: unknown activation %d", act);
+  DSP_REQUIRE(act >= 0 && act <= 2, "dsp_moe_product: unknown activation %d", act);
+  DSP_REQUIRE(act != 2 || N % 2 == 0, "dsp_moe_product: a gated unit needs an even number of columns, not %d", N);
+  DSP_REQUIRE(act == 2 || !row_scale, "dsp_moe_product: row factors come with the gated unit only");
   if (tensor_cores) {
     DSP_REQUIRE(ab_dtype == DSP_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)B % 16) == 0,
                 "dsp_moe_product: the tensor-core kernel takes 16-byte aligned bfloat16 operands with K and the row "
@@ -407,11 +451,11 @@ extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int*
     if (tensor_cores == 2)
       DSP_CUDA(launch_plain(moe_product_mma_kernel<MMA_ROWS_WIDE, 3>, mgrid, dim3(MMA_ROWS_WIDE * 2), mma_smem_bytes(MMA_ROWS_WIDE, 3),
                             stream, (const bf16*)A, lda, a_rows, a_div, (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert,
-                            tile_row0, tile_rows, n_tiles, N, K, act));
+                            tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
     else
       DSP_CUDA(launch_plain(moe_product_mma_kernel<MMA_ROWS, 4>, mgrid, dim3(MMA_ROWS * 2), mma_smem_bytes(MMA_ROWS, 4), stream,
                             (const bf16*)A, lda, a_rows, a_div, (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert,
-                            tile_row0, tile_rows, n_tiles, N, K, act));
+                            tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
     DSP_CHECK_LAUNCH("dsp_moe_product (tensor cores)");
     return 0;
   }
@@ -419,24 +463,24 @@ extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int*
   DSP_REQUIRE(grid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
   if (ab_dtype == DSP_F32) {
     DSP_CUDA(launch_plain(moe_product_kernel<float>, grid, dim3(256), 0, stream, (const float*)A, lda, a_rows, a_div,
-                          (const float*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
+                          (const float*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
   } else {
     DSP_CUDA(launch_plain(moe_product_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)A, lda, a_rows, a_div,
-                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
+                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
   }
   DSP_CHECK_LAUNCH("dsp_moe_product");
   return 0;
 }
 
-extern "C" int dsp_moe_combine(const float* P, long ldp, const float* wts, const int* ids, float* y, long ldy, long T,
-                               int top, int width, cudaStream_t stream) {
+extern "C" int dsp_moe_combine(const float* P, long ldp, const float* wts, const int* ids, const float* base, long ldb,
+                               float* y, long ldy, long T, int top, int width, cudaStream_t stream) {
   if (T == 0) return 0;
-  DSP_REQUIRE(P && wts && ids && y, "dsp_moe_combine: missing operand");
+  DSP_REQUIRE(P && ids && y, "dsp_moe_combine: missing operand");
   const long n = T * width;
   const int sms = dsp_num_sms();
   const long want = (n + 255) / 256, cap = (long)(sms > 0 ? sms : 148) * 16;
   DSP_CUDA(launch_plain(moe_combine_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, P, ldp,
-                        wts, ids, y, ldy, T, top, width));
+                        wts, ids, base, ldb, y, ldy, T, top, width));
   DSP_CHECK_LAUNCH("dsp_moe_combine");
   return 0;
 }

@@ -149,15 +149,18 @@ layer_norm_kernel(const void* __restrict__ x, int x_dtype, long ldx, const float
 //
 //     x <- x + d,   d = y * scale[i] * sigmoid(gate)        (gate given: a gated, scaled sublayer)
 //                   d = y / sqrt(mean(y^2) + eps) * rms_w   (rms_w given: an RMS-normed addend)
-//                   d = y                                   (neither)
-//     out = layer_norm(x) * norm_w  (norm_w given)  or  x   (out given without norm_w)
+//                   d = y                                   (neither; y may be missing: d = 0)
+//     and d += bias[i] when a row `bias` is given (the same for every row),
+//     out = layer_norm(x) * norm_w  (norm_w given; with `norm_rms` the RMS norm
+//           x / sqrt(mean(x^2) + eps) * norm_w instead)  or  x   (out given without norm_w)
 //
 // One block per row; the new row stays in shared memory between the passes.
 __global__ void __launch_bounds__(256)
 stream_update_kernel(float* __restrict__ x32, long ldx, const void* __restrict__ y, int y_dtype, long ldy,
                      const void* __restrict__ gate, int g_dtype, long ldg, const float* __restrict__ scale,
-                     const float* __restrict__ rms_w, float rms_eps, const float* __restrict__ norm_w,
-                     float norm_eps, void* __restrict__ out, int out_dtype, long ldo, int width) {
+                     const float* __restrict__ rms_w, float rms_eps, const float* __restrict__ bias,
+                     const float* __restrict__ norm_w, float norm_eps, int norm_rms, void* __restrict__ out,
+                     int out_dtype, long ldo, int width) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
   const size_t r = blockIdx.x;
@@ -172,13 +175,14 @@ stream_update_kernel(float* __restrict__ x32, long ldx, const void* __restrict__
   }
   float s = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float d = ld_any(y, y_dtype, r * ldy + i);
+    float d = y ? ld_any(y, y_dtype, r * ldy + i) : 0.f;
     if (gate) {
       const float g = ld_any(gate, g_dtype, r * ldg + i);
       d *= (scale ? scale[i] : 1.f) * (1.f / (1.f + expf(-g)));
     } else if (rms_w) {
       d *= inv_rms * rms_w[i];
     }
+    if (bias) d += bias[i];
     const float v = x32[r * ldx + i] + d;
     x32[r * ldx + i] = v;
     row[i] = v;
@@ -190,7 +194,7 @@ stream_update_kernel(float* __restrict__ x32, long ldx, const void* __restrict__
     for (int i = threadIdx.x; i < width; i += blockDim.x) st_any(out, out_dtype, r * ldo + i, row[i]);
     return;
   }
-  const float mean = block_sum(s, scratch) / (float)width;
+  const float mean = norm_rms ? 0.f : block_sum(s, scratch) / (float)width;
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float d = row[i] - mean;
@@ -348,17 +352,18 @@ extern "C" int dsp_layer_norm(const void* x, int x_dtype, long ldx, const float*
 
 extern "C" int dsp_stream_update(float* x32, long ldx, const void* y, int y_dtype, long ldy, const void* gate,
                                  int g_dtype, long ldg, const float* scale, const float* rms_w, float rms_eps,
-                                 const float* norm_w, float norm_eps, void* out, int out_dtype, long ldo,
-                                 int n_rows, int width, cudaStream_t stream) {
+                                 const float* bias, const float* norm_w, float norm_eps, int norm_rms, void* out,
+                                 int out_dtype, long ldo, int n_rows, int width, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  DSP_REQUIRE(x32 && y && width > 0, "dsp_stream_update: missing operand");
+  DSP_REQUIRE(x32 && width > 0, "dsp_stream_update: missing operand");
+  DSP_REQUIRE(y || (!gate && !rms_w), "dsp_stream_update: a gate or a norm but no addend");
   DSP_REQUIRE(!(gate && rms_w), "dsp_stream_update: an addend is gated or RMS-normed, not both");
   const size_t smem = (size_t)width * sizeof(float);
   DSP_REQUIRE(smem <= 200 * 1024, "dsp_stream_update: a row of %d values does not fit shared memory", width);
   static size_t configured = 48 * 1024;
   DSP_REQUIRE(row_smem((const void*)stream_update_kernel, smem, &configured) == 0, "dsp_stream_update: shared memory opt-in failed");
   DSP_CUDA(launch_plain(stream_update_kernel, dim3(n_rows), dim3(256), smem, stream, x32, ldx, y, y_dtype, ldy, gate,
-                        g_dtype, ldg, scale, rms_w, rms_eps, norm_w, norm_eps, out, out_dtype, ldo, width));
+                        g_dtype, ldg, scale, rms_w, rms_eps, bias, norm_w, norm_eps, norm_rms, out, out_dtype, ldo, width));
   DSP_CHECK_LAUNCH("dsp_stream_update");
   return 0;
 }

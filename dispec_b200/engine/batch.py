@@ -88,6 +88,7 @@ class StepContext:
         self.num_fed = 0  # single tokens whose value comes from the previous step on the device
         self.graph_capture = False  # host-side choices must not depend on the step's values
         self.scratch: dict = {}
+        self.layer_trace = None  # a list: the model appends a copy of the stream after every layer run
 
     def cache_view(self, placement, write: bool) -> LayerCacheView:
         g = placement.group

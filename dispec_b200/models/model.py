@@ -52,6 +52,9 @@ class DecoderModel:
         self.layers = [build_part(s, built, self._bindings) for s in spec.layers]
         self.final_norm = build_part(spec.final_norm, built, self._bindings)
         self.head = build_part(spec.head, built, self._bindings)
+        self.pass_entry = build_part(spec.pass_entry, built, self._bindings) if spec.pass_entry is not None else None
+        if self.pass_entry is None and any(c.entry is not None for c in spec.schedule):
+            raise ValueError("the schedule marks the start of a pass but the model has no pass_entry part")
         self._parts = list(built.values())
         self.schedule: list[LayerCall] = list(spec.schedule)
         self._plan_caches()
@@ -135,19 +138,33 @@ class DecoderModel:
         output not yet added to it."""
         x = self.embedding.forward(ctx)
         pending = None
+        # what the embedding gave, for passes that take it in again (the stream is updated in place)
+        x0 = x.full.clone() if self.pass_entry is not None and self.pass_entry.needs_embedding else None
+        trace = getattr(ctx, "layer_trace", None)
         for idx, call in enumerate(self.schedule):
+            if call.entry is not None:
+                if pending is not None:
+                    raise ValueError(f"schedule entry {idx}: a pass begins while a block's result is still pending")
+                offer = getattr(self.layers[call.layer], "first_norm_after_product", None)
+                pending = self.pass_entry.forward(ctx, x, x0, call.entry,
+                                                  then_norm=offer() if offer is not None else None)
             label = self.call_cache[idx]
             cache = ctx.cache_view(self.placement[label], call.write) if label is not None else None
             sidx = self.call_state[idx]
             state = ctx.state_view(sidx) if sidx is not None else None
             # a block may take its first norm from the product that wrote x (see PreNormBlock)
-            nxt = self.layers[self.schedule[idx + 1].layer] if idx + 1 < len(self.schedule) else None
+            # (not across the start of a pass: the stream changes there before the norm reads it)
+            nxt = None
+            if idx + 1 < len(self.schedule) and self.schedule[idx + 1].entry is None:
+                nxt = self.layers[self.schedule[idx + 1].layer]
             offer = getattr(nxt, "first_norm_after_product", None)
             then_norm = offer() if offer is not None else None
             if then_norm is not None and hasattr(self.layers[call.layer], "first_norm_after_product"):
                 x, pending = self.layers[call.layer].forward(ctx, x, pending, cache, state, then_norm=then_norm)
             else:
                 x, pending = self.layers[call.layer].forward(ctx, x, pending, cache, state)
+            if trace is not None:  # tests and debugging: the 32-bit stream after every layer run
+                trace.append((x.full if hasattr(x, "full") else x).clone())
         return x, pending
 
     def logits(self, ctx, x, pending, rows: torch.Tensor) -> torch.Tensor:

@@ -3,7 +3,9 @@ the order in which the layers run.
 
 ``ModelSpec.schedule`` is data: a list of ``LayerCall``.  A layer may be named twice (its
 weights run again, each call with a cache of its own) and a call may read the cache another
-call wrote (``cache`` equal to that call's, ``write=False``).
+call wrote (``cache`` equal to that call's, ``write=False``).  A run of layers that is passed
+over several times lists its calls once per pass; the first call of pass t carries ``entry=t``, and
+the part ``ModelSpec.pass_entry`` (role "stream_input") says what enters the stream there.
 """
 from __future__ import annotations
 
@@ -17,6 +19,7 @@ class LayerCall:
     layer: int  # index into ModelSpec.layers
     cache: int | None = None  # label of the layer cache this call uses (None: the call's own index)
     write: bool = True  # False: read-only use of a cache another call writes
+    entry: int | None = None  # t: pass t over a run of repeated layers begins here (``ModelSpec.pass_entry`` runs first)
 
 
 @dataclass
@@ -27,6 +30,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     schedule: list[LayerCall] = field(default_factory=list)
+    pass_entry: PartSpec | None = None  # what enters the stream where a ``LayerCall`` has an ``entry``
     optional_tensors: frozenset = frozenset()  # checkpoint names that may be present and are ignored
     vocab_size: int = 0
     max_position: int = 0

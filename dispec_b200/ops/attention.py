@@ -36,14 +36,18 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor
                             page_table: torch.Tensor, positions: torch.Tensor,
                             seq_of_token: torch.Tensor, out: torch.Tensor, num_heads: int,
                             num_kv_heads: int, head_dim: int, window: int, scale: float,
-                            sink: bool = False) -> torch.Tensor:
+                            sink: bool = False, chunked: bool = False, sink_values: torch.Tensor | None = None,
+                            turn_freq: torch.Tensor | None = None) -> torch.Tensor:
     """32-bit arithmetic kernel, any value size up to 512 and any group size.
 
     q: element (t, h, d) at q.data_ptr + (t * q_stride + h * D + d); out: [T, H * Dv], Dv being the
     width of the value pool (it may differ from the keys' D).
     The query at absolute position p = positions[t] sees keys max(0, p-window+1)..p
-    (window 0: from 0) of sequence seq_of_token[t].  ``sink``: the softmax has one more key of
-    score 0 and no value (weights exp(s_j) / (1 + sum exp(s_j))).
+    (window 0: from 0) of sequence seq_of_token[t]; with ``chunked`` the keys of its own chunk of
+    ``window`` positions, floor(p / window) * window .. p.  ``sink``: the softmax has one more key
+    of score 0 and no value (weights exp(s_j) / (1 + sum exp(s_j))); with ``sink_values`` (float32
+    [H]) that key's score is the head's own number, unscaled.  ``turn_freq`` (float32 [Dv/2]):
+    every head's result is turned back, pair (m, m + Dv/2) by -p * turn_freq[m].
     """
     assert q.is_cuda and k_pool.is_cuda, "CUDA tensors only (there is no CPU path)"
     T = positions.shape[0]
@@ -54,12 +58,23 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor
     assert out.is_contiguous() and out.shape == (T, num_heads * dv) and out.dtype == q.dtype
     assert page_table.dtype == torch.int32 and page_table.stride(1) == 1
     assert positions.dtype == torch.int32 and seq_of_token.dtype == torch.int32
+    _check_sink_turn(sink, sink_values, turn_freq, num_heads, dv)
     L.check(L.core().dsp_attn_generic(
         L.ptr(q), L.i64(q_stride), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table),
         page_table.stride(0), L.ptr(positions), L.ptr(seq_of_token), L.ptr(out),
         L.i64(out.stride(0)), T, num_heads, num_kv_heads, head_dim, dv, page_size, num_pages,
-        window, L.f32(scale), int(sink), L.dtype_code(q.dtype), L.stream_handle()))
+        window, int(bool(chunked) and window > 0), L.f32(scale), int(bool(sink)), L.ptr(sink_values),
+        L.ptr(turn_freq), L.dtype_code(q.dtype), L.stream_handle()))
     return out
+
+
+def _check_sink_turn(sink, sink_values, turn_freq, num_heads: int, value_dim: int) -> None:
+    if sink_values is not None:
+        assert sink, "sink_values without a sink"
+        assert sink_values.dtype == torch.float32 and sink_values.is_contiguous() and sink_values.shape == (num_heads,)
+    if turn_freq is not None:
+        assert value_dim % 2 == 0 and turn_freq.dtype == torch.float32 and turn_freq.is_contiguous()
+        assert turn_freq.shape[0] >= value_dim // 2
 
 
 _MMA_ERRORS = {1: "launch failed", 2: "unsupported head/group/split counts",
@@ -296,13 +311,21 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
 def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, cache,
                      inv_freq: torch.Tensor | None, rotary_dim: int, num_heads: int, num_kv_heads: int,
                      key_dim: int, value_dim: int, out_dtype: torch.dtype, v_other: torch.Tensor | None = None,
-                     blend: torch.Tensor | None = None) -> torch.Tensor:
+                     blend: torch.Tensor | None = None, q_norm: torch.Tensor | None = None,
+                     k_norm: torch.Tensor | None = None, norm_eps: float = 0.0, v_norm: bool = False,
+                     v_inv_freq: torch.Tensor | None = None) -> torch.Tensor:
     """From rows [q (H x Dk) | k (G x Dk) | v (G x Dv)] of a fused projection: turns pairs
     (i, i + rotary_dim/2) of every query and key head by position * inv_freq[i] in 32-bit, blends
     v <- (1 - blend) v + blend * v_other when ``v_other`` [T, G * Dv] is given (``blend``: a float32
     scalar on the device), stores key and value into the pages of ``cache`` (its "key" and "value"
     pools, of widths Dk and Dv) when the cache is written by this call, and returns the turned
-    queries [T, H * Dk] in ``out_dtype``.  Rows with a negative position are skipped."""
+    queries [T, H * Dk] in ``out_dtype``.  Rows with a negative position are skipped.
+
+    ``q_norm`` / ``k_norm`` (float32 [Dk], one weight for all heads): every query / key head is
+    divided by its root mean square (``norm_eps`` inside the root) and multiplied by the weight
+    before it is turned.  ``v_norm``: every value head is divided by its root mean square (no
+    weight).  ``v_inv_freq`` (float32 [Dv/2]): the value of position p is stored turned, pair
+    (m, m + Dv/2) by p * v_inv_freq[m], after the norm."""
     if not qkv.is_cuda:
         raise L.KernelError("qkv_rotate_store: CUDA tensors only (there is no CPU path)")
     T = qkv.shape[0]
@@ -319,6 +342,11 @@ def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: t
     if v_other is not None:
         assert blend is not None and blend.dtype == torch.float32 and blend.numel() == 1 and blend.is_cuda
         assert v_other.shape == (T, G * dv) and v_other.stride(1) == 1
+    for w in (q_norm, k_norm):
+        assert w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.shape == (dk,))
+    if v_inv_freq is not None:
+        assert dv % 2 == 0 and v_inv_freq.dtype == torch.float32 and v_inv_freq.is_contiguous()
+        assert v_inv_freq.shape[0] >= dv // 2
     q_out = torch.empty((T, H * dk), dtype=out_dtype, device=qkv.device)
     lib = L.mixer_library("attn_sink")
     L.check(lib.dsp_qkv_rotate_store(
@@ -326,7 +354,7 @@ def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: t
         L.ptr(table), table.stride(0), L.ptr(k_pool), L.ptr(v_pool), L.dtype_code(out_dtype), L.ptr(inv_freq),
         rotary_dim, L.ptr(v_other), L.dtype_code(v_other.dtype) if v_other is not None else 0,
         L.i64(v_other.stride(0) if v_other is not None else 0), L.ptr(blend if v_other is not None else None),
-        L.ptr(q_out), L.i64(q_out.stride(0)), T, H, G, dk, dv, page_size, num_pages, int(cache.write),
+        L.ptr(q_norm), L.ptr(k_norm), L.f32(norm_eps), int(bool(v_norm)), L.ptr(v_inv_freq), L.ptr(q_out), L.i64(q_out.stride(0)), T, H, G, dk, dv, page_size, num_pages, int(cache.write),
         L.stream_handle()))
     return q_out
 
@@ -360,22 +388,28 @@ def sink_choose_splits(num_single: int, num_kv_heads: int, keys: int, device=Non
 
 
 def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0, num_tiles, out,
-                         num_heads, num_kv_heads, window, scale, sink, num_single: int = 0, splits: int = 1) -> torch.Tensor:
+                         num_heads, num_kv_heads, window, scale, sink, num_single: int = 0, splits: int = 1,
+                         chunked: bool = False, sink_values: torch.Tensor | None = None,
+                         turn_freq: torch.Tensor | None = None, positions: torch.Tensor | None = None) -> torch.Tensor:
     """The tensor-core kernel over a tile list (``tokens per tile`` = 64 // group).  The first
     ``num_single`` tiles are single tokens (the first rows of the batch): with ``splits`` > 1
-    their keys are cut into that many shares, merged by the combine kernel."""
+    their keys are cut into that many shares, merged by the combine kernel.  ``chunked``,
+    ``sink_values``, ``turn_freq``: as in ``paged_attention_generic``; ``positions`` (of the step's
+    tokens) is needed where split results are turned back."""
     num_pages, G, page_size, dk = k_pool.shape
     dv = v_pool.shape[3]
     assert q.dtype == k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and q.stride(1) == 1 and out.stride(1) == 1
     fn = getattr(L.sink_attention_library(dk, dv), f"dsp_attn_sink_mma_k{dk}_v{dv}")
     tpt = SINK_ROWS_PER_TILE // (num_heads // num_kv_heads)
+    _check_sink_turn(sink, sink_values, turn_freq, num_heads, dv)
+    mask_mode = int(bool(chunked) and window > 0)
 
     def launch(offset, count, n_splits, part_o, part_ml):
         rc = fn(L.ptr(q), L.i64(q.stride(0)), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table), page_table.stride(0),
                 L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), offset, count, L.ptr(out),
-                L.i64(out.stride(0)), num_heads, num_kv_heads, tpt, page_size, num_pages, window, L.f32(scale),
-                int(sink), n_splits, L.ptr(part_o), L.ptr(part_ml), ctypes.c_void_p(_device_error_address(q.device)),
+                L.i64(out.stride(0)), num_heads, num_kv_heads, tpt, page_size, num_pages, window, mask_mode,
+                L.f32(scale), int(bool(sink)), L.ptr(sink_values), L.ptr(turn_freq), n_splits, L.ptr(part_o), L.ptr(part_ml), ctypes.c_void_p(_device_error_address(q.device)),
                 L.stream_handle())
         L.LaunchCounter.n += 1
         if rc != 0:
@@ -385,8 +419,15 @@ def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_s
     if num_single > 0 and splits > 1:
         part_o, part_ml = _partial_buffers(q.device, num_single * num_heads, splits, dv)
         launch(0, num_single, splits, part_o, part_ml)
-        L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out), L.i64(out.stride(0)), num_single,
-                                          num_heads, dv, splits, L.dtype_code(out.dtype), L.stream_handle()))
+        if turn_freq is not None:
+            assert positions is not None and positions.dtype == torch.int32
+            L.check(L.mixer_library("attn_sink").dsp_attn_combine_turn(
+                L.ptr(part_o), L.ptr(part_ml), L.ptr(out), L.dtype_code(out.dtype), L.i64(out.stride(0)),
+                L.ptr(positions), L.ptr(turn_freq), num_single, num_heads, dv, splits, L.stream_handle()))
+        else:
+            L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out), L.i64(out.stride(0)),
+                                              num_single, num_heads, dv, splits, L.dtype_code(out.dtype),
+                                              L.stream_handle()))
         first = num_single
     if num_tiles > first:
         launch(first, num_tiles - first, 1, None, None)
@@ -394,11 +435,14 @@ def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_s
 
 
 def sink_paged_attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, num_heads: int, num_kv_heads: int,
-                         key_dim: int, value_dim: int, window: int, scale: float, sink: bool) -> torch.Tensor:
+                         key_dim: int, value_dim: int, window: int, scale: float, sink: bool, chunked: bool = False,
+                         sink_values: torch.Tensor | None = None, turn_freq: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of the step over pools whose keys and values have widths of their own, with an
     optional sink in the softmax: q [T, H * Dk] (already turned), out [T, H * Dv].  bfloat16 runs
     on the tensor-core kernel where it is built for the sizes and the batch lists its tiles;
-    everything else (and float32 always) on the 32-bit kernel."""
+    everything else (and float32 always) on the 32-bit kernel.  ``chunked``: ``window`` is the
+    size of the chunks a position's keys come from; ``sink_values``: the sink's score per head;
+    ``turn_freq``: results are turned back by the query's position (``paged_attention_generic``)."""
     group = num_heads // num_kv_heads
     tpt = sink_tokens_per_tile(group, key_dim, value_dim)
     if q.dtype == torch.bfloat16 and tpt is not None and tpt in ctx.attention_tiles:
@@ -407,7 +451,9 @@ def sink_paged_attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, num_hea
         splits = sink_choose_splits(ctx.num_decode_seqs, num_kv_heads, keys, q.device)
         return sink_attention_tiles(q, cache.key_pool, cache.value_pool, cache.page_table, ctx.q_start, ctx.ctx_len,
                                     tile_seq, tile_tok0, num_tiles, out, num_heads, num_kv_heads, window, scale, sink,
-                                    num_single=ctx.num_decode_seqs, splits=splits)
+                                    num_single=ctx.num_decode_seqs, splits=splits, chunked=chunked,
+                                    sink_values=sink_values, turn_freq=turn_freq, positions=ctx.positions)
     return paged_attention_generic(q, q.stride(0), cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads, key_dim,
-                                   window, scale, sink=sink)
+                                   window, scale, sink=sink, chunked=chunked, sink_values=sink_values,
+                                   turn_freq=turn_freq)

@@ -13,9 +13,10 @@ def _lib():
     return L.mixer_library("moe")
 
 
-def route(h: torch.Tensor, w_router: torch.Tensor, groups: int, keep: int, top: int):
+def route(h: torch.Tensor, w_router: torch.Tensor, groups: int, keep: int, top: int, score: str = "softmax"):
     """h [T, W] (either type), w_router float32 [E, W] -> (ids int32 [T, top], weights float32
-    [T, top]): softmax over all experts in 32-bit; the ``top`` largest scores among the experts
+    [T, top]): softmax over all experts in 32-bit (``score`` "sigmoid": the sigmoid of every
+    expert's logit instead); the ``top`` largest scores among the experts
     of the ``keep`` groups (of ``groups`` equal runs of neighbours) with the largest best score;
     the weights are those scores."""
     if not (h.is_cuda and w_router.is_cuda):
@@ -27,7 +28,8 @@ def route(h: torch.Tensor, w_router: torch.Tensor, groups: int, keep: int, top: 
     ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
     L.check(_lib().dsp_moe_route(L.ptr(h), L.dtype_code(h.dtype), L.i64(h.stride(0)), L.ptr(w_router), T, W, E,
-                                 groups, keep, top, L.ptr(ids), L.ptr(wts), L.stream_handle()))
+                                 groups, keep, top, {"softmax": 0, "sigmoid": 1}[score], L.ptr(ids), L.ptr(wts),
+                                 L.stream_handle()))
     return ids, wts
 
 
@@ -70,28 +72,48 @@ def plan(ids: torch.Tensor, num_experts: int, tensor_cores: bool = False) -> Exp
 
 
 def expert_product(p: ExpertPlan, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *,
-                   rows_are_tokens: bool, scatter: bool, square_relu: bool = False) -> torch.Tensor:
+                   rows_are_tokens: bool, scatter: bool, square_relu: bool = False,
+                   clamped_glu: tuple | None = None, row_scale: torch.Tensor | None = None) -> torch.Tensor:
     """C = act(A W_e^T) for every pair, with its expert's matrix (w: [E, N, K]).  ``rows_are_tokens``:
     A holds one row per token (a pair reads its token's row); otherwise one row per sorted place.
     ``scatter``: the result row of a pair goes to its pair index t * top + k; otherwise to its
-    sorted place.  Returns [pairs, N]."""
+    sorted place.  Returns [pairs, N].
+
+    ``clamped_glu`` = (limit, alpha): the rows of every W_e alternate between a gate matrix and an
+    up matrix (row 2j: gate j, row 2j + 1: up j) and the result is the gated unit
+    min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1), [pairs, N / 2];
+    ``row_scale`` (float32 [pairs], by pair index t * top + k; needs ``rows_are_tokens``): a factor
+    on the pair's input row, applied to the 32-bit sums g and u before the clamps."""
     assert a.dim() == 2 and a.stride(1) == 1 and w.dim() == 3 and w.is_contiguous() and a.dtype == w.dtype
     E, N, K = w.shape
-    assert a.shape[1] == K
-    out = torch.empty((max(p.num_pairs, 1), N), dtype=out_dtype, device=a.device)
+    assert a.shape[1] == K and not (square_relu and clamped_glu)
+    act, limit, alpha = (1 if square_relu else 0), 0.0, 0.0
+    if clamped_glu is not None:
+        act, (limit, alpha) = 2, clamped_glu
+        assert N % 2 == 0
+    if row_scale is not None:
+        assert clamped_glu is not None and rows_are_tokens
+        assert row_scale.dtype == torch.float32 and row_scale.is_contiguous() and row_scale.numel() == p.num_pairs
+    out = torch.empty((max(p.num_pairs, 1), N // 2 if act == 2 else N), dtype=out_dtype, device=a.device)
     L.check(_lib().dsp_moe_product(
         L.ptr(a), L.dtype_code(a.dtype), L.i64(a.stride(0)), L.ptr(p.sorted_pair if rows_are_tokens else None),
         p.top if rows_are_tokens else 1, L.ptr(w), L.ptr(out), L.dtype_code(out_dtype), L.i64(out.stride(0)),
         L.ptr(p.sorted_pair if scatter else None), L.ptr(p.tiles[0]), L.ptr(p.tiles[1]), L.ptr(p.tiles[2]),
-        L.ptr(p.n_tiles), p.max_tiles, N, K, int(square_relu), int(p.tensor_cores), L.stream_handle()))
+        L.ptr(p.n_tiles), p.max_tiles, N, K, act, L.ptr(row_scale), L.f32(limit), L.f32(alpha), int(p.tensor_cores),
+        L.stream_handle()))
     return out[:p.num_pairs]
 
 
-def combine(pair_rows: torch.Tensor, wts: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-    """y[t] = sum over k of wts[t, k] * pair_rows[t * top + k] (float32)."""
+def combine(pair_rows: torch.Tensor, wts: torch.Tensor | None, ids: torch.Tensor,
+            base: torch.Tensor | None = None) -> torch.Tensor:
+    """y[t] = base[t] + sum over k of wts[t, k] * pair_rows[t * top + k] (float32); without
+    ``wts`` every weight is 1, without ``base`` the sum starts from 0."""
     T, top = ids.shape
     assert pair_rows.dtype == torch.float32 and pair_rows.stride(1) == 1 and pair_rows.shape[0] == T * top
+    if base is not None:
+        assert base.dtype == torch.float32 and base.stride(1) == 1 and base.shape == (T, pair_rows.shape[1])
     y = torch.empty((T, pair_rows.shape[1]), dtype=torch.float32, device=pair_rows.device)
-    L.check(_lib().dsp_moe_combine(L.ptr(pair_rows), L.i64(pair_rows.stride(0)), L.ptr(wts), L.ptr(ids), L.ptr(y),
+    L.check(_lib().dsp_moe_combine(L.ptr(pair_rows), L.i64(pair_rows.stride(0)), L.ptr(wts), L.ptr(ids), L.ptr(base),
+                                   L.i64(base.stride(0) if base is not None else 0), L.ptr(y),
                                    L.i64(y.stride(0)), L.i64(T), top, pair_rows.shape[1], L.stream_handle()))
     return y

@@ -96,28 +96,34 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: tor
     return y
 
 
-def stream_update(x32: torch.Tensor, y: torch.Tensor, *, gate: torch.Tensor | None = None,
+def stream_update(x32: torch.Tensor, y: torch.Tensor | None, *, gate: torch.Tensor | None = None,
                   scale: torch.Tensor | None = None, rms_weight: torch.Tensor | None = None, rms_eps: float = 0.0,
-                  norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
-                  out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+                  bias: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
+                  norm_kind: str = "layer", out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
     """x32 += d in place (float32 rows), with d = y * scale * sigmoid(gate) when ``gate`` is given,
-    d = y / sqrt(mean(y^2) + rms_eps) * rms_weight when ``rms_weight`` is, else d = y.  With
-    ``out_dtype``: also returns the layer norm of the new rows times ``norm_weight`` (or, without
-    ``norm_weight``, the new rows themselves) in that type."""
+    d = y / sqrt(mean(y^2) + rms_eps) * rms_weight when ``rms_weight`` is, else d = y (``y`` None:
+    0); ``bias`` (float32 [width]) is added to every row as well.  With ``out_dtype``: also returns
+    the norm of the new rows times ``norm_weight`` (``norm_kind`` "layer": mean taken off; "rms":
+    x / sqrt(mean(x^2) + norm_eps)) or, without ``norm_weight``, the new rows themselves, in that type."""
     _rows2d(x32, "stream_update")
-    _rows2d(y, "stream_update")
-    assert x32.dtype == torch.float32 and y.shape == x32.shape
+    assert x32.dtype == torch.float32
+    if y is not None:
+        _rows2d(y, "stream_update")
+        assert y.shape == x32.shape
+    assert norm_kind in ("layer", "rms")
     width = x32.shape[1]
-    for v in (scale, rms_weight, norm_weight):
+    for v in (scale, rms_weight, norm_weight, bias):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.shape == (width,))
     if gate is not None:
         _rows2d(gate, "stream_update")
         assert gate.shape == x32.shape
     out = torch.empty(x32.shape, dtype=out_dtype, device=x32.device) if out_dtype is not None else None
     L.check(L.core().dsp_stream_update(
-        L.ptr(x32), L.i64(x32.stride(0)), L.ptr(y), L.dtype_code(y.dtype), L.i64(y.stride(0)), L.ptr(gate),
+        L.ptr(x32), L.i64(x32.stride(0)), L.ptr(y), L.dtype_code(y.dtype) if y is not None else 0,
+        L.i64(y.stride(0) if y is not None else 0), L.ptr(gate),
         L.dtype_code(gate.dtype) if gate is not None else 0, L.i64(gate.stride(0) if gate is not None else 0),
-        L.ptr(scale), L.ptr(rms_weight), L.f32(rms_eps), L.ptr(norm_weight), L.f32(norm_eps), L.ptr(out),
+        L.ptr(scale), L.ptr(rms_weight), L.f32(rms_eps), L.ptr(bias), L.ptr(norm_weight), L.f32(norm_eps),
+        int(norm_kind == "rms"), L.ptr(out),
         L.dtype_code(out_dtype) if out is not None else 0, L.i64(out.stride(0) if out is not None else 0),
         x32.shape[0], width, L.stream_handle()))
     return out

@@ -1,6 +1,7 @@
 """Grouped-query attention over the paged cache: ``gqa_attention`` (keys and values of one
-width, plain softmax) and ``sink_attention`` (widths of their own, an optional sink in the
-softmax, values optionally blended with another layer's; at the end of this file).
+width, plain softmax) and ``sink_attention`` (widths of their own, a window or a chunked mask,
+an optional sink in the softmax, optional norms of the heads, values optionally blended with
+another layer's or turned by their positions; at the end of this file).
 
 q, k, v = h W^T + b (one fused product, rows ordered q, k, v: puneethgv/DiSpec
 dispec/engine/model_runner.py:104-118,131-136); rotation of q and k and the write of k, v
@@ -123,11 +124,24 @@ class SinkAttention(Mixer):
     of the step's tokens under ``key``; one with role "blend" replaces its own by
     (1 - m) v + m v_source, m being its tensor ``value_mix`` (a scalar), before they are cached and
     used.  A source owns the tensor too (unused), so that checkpoints list it for every such layer.
-    Scores, softmax, angles and the blend are 32-bit; the projections return 32-bit rows, which
-    are rounded once, after the rotation and the blend, when they enter the cache."""
+
+    ``mask``: "window" (above) or "chunk": position p sees the keys j <= p of its own chunk,
+    floor(j / window) = floor(p / window), chunks counted from position 0 of the sequence.
+    ``sink``: True (above), False, or "learned": the extra key's score is the head's number z_h
+    (tensor ``sink`` [H], unscaled): weights exp(s_j) / (exp(z_h) + sum_j exp(s_j)).
+    ``head_norm``: every query and key head is divided by its root mean square (``norm_eps`` inside
+    the root) and multiplied by ``q.norm.weight`` / ``k.norm.weight`` ([key_dim], one for all heads)
+    before it is turned.  ``value_norm``: every value head is divided by its root mean square (no
+    weight).  ``value_theta``: the value of position j is cached turned, pair (m, m + value_dim/2)
+    by the angle j * value_theta^(-2m / value_dim), after its norm; every head's result at position
+    p is turned back by -p times the same angles, so that a value enters the sum turned by p - j.
+    Scores, softmax, angles, norms and the blend are 32-bit; the projections return 32-bit rows,
+    which are rounded once, after norm, rotation and blend, when they enter the cache."""
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
-                 scale: float, position_encoding, window: int = 0, sink: bool = True, value_mix=None):
+                 scale: float, position_encoding, window: int = 0, sink=True, value_mix=None,
+                 mask: str = "window", head_norm: bool = False, value_norm: bool = False, norm_eps: float = 0.0,
+                 value_theta: float | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         if not float(scale) > 0.0:
@@ -136,10 +150,21 @@ class SinkAttention(Mixer):
             raise ValueError(f"value_mix must be None or ('source' | 'blend', key), got {value_mix!r}")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
         self.key_dim, self.value_dim = key_dim, value_dim
-        self.scale, self.window, self.sink = float(scale), int(window), bool(sink)
+        if sink not in (True, False, "learned"):
+            raise ValueError(f"sink must be True, False or 'learned', got {sink!r}")
+        if mask not in ("window", "chunk"):
+            raise ValueError(f"mask must be 'window' or 'chunk', got {mask!r}")
+        if value_theta is not None and (value_dim % 2 or not float(value_theta) > 0):
+            raise ValueError(f"values of width {value_dim} cannot be turned with base {value_theta}")
+        if value_mix is not None and value_norm:
+            raise ValueError("sink_attention: values are blended or normed, not both")
+        self.scale, self.window, self.sink = float(scale), int(window), sink
+        self.mask, self.head_norm, self.value_norm = mask, bool(head_norm), bool(value_norm)
+        self.norm_eps = float(norm_eps)
+        self.value_theta = float(value_theta) if value_theta is not None else None
         self.position_encoding = position_encoding
         self.value_mix = tuple(value_mix) if value_mix is not None else None
-        self.w_qkv = self.w_o = self.blend = None
+        self.w_qkv = self.w_o = self.blend = self.q_norm = self.k_norm = self.sink_values = self.value_freq = None
 
     def tensor_specs(self):
         h, H, G, dk, dv = self.hidden_size, self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
@@ -147,14 +172,27 @@ class SinkAttention(Mixer):
                  "v.weight": TensorSpec((G * dv, h)), "o.weight": TensorSpec((h, H * dv))}
         if self.value_mix is not None:
             specs["value_mix"] = TensorSpec((), dtype="float32")
+        if self.head_norm:
+            specs["q.norm.weight"] = TensorSpec((dk,), dtype="float32", init="one_plus_normal")
+            specs["k.norm.weight"] = TensorSpec((dk,), dtype="float32", init="one_plus_normal")
+        if self.sink == "learned":
+            specs["sink"] = TensorSpec((H,), dtype="float32")
         return specs
 
     def load(self, tensors):
         self.w_qkv = torch.cat([tensors["q.weight"], tensors["k.weight"], tensors["v.weight"]], dim=0).contiguous()
         self.w_o = tensors["o.weight"]
         self.blend = tensors.get("value_mix")
+        self.q_norm, self.k_norm = tensors.get("q.norm.weight"), tensors.get("k.norm.weight")
+        self.sink_values = tensors.get("sink")
+
+    def prepare(self, device):
+        if self.value_theta is not None:  # the nearest float32 to theta^(-2m / value_dim)
+            exponent = torch.arange(0, self.value_dim, 2, dtype=torch.float64) / self.value_dim
+            self.value_freq = (1.0 / (self.value_theta ** exponent)).to(torch.float32).to(device)
 
     def cache_need(self):
+        # a chunk's keys all lie within the last `window` positions: pages behind them are given back
         return CacheNeed((CacheTensor("key", self.num_kv_heads, self.key_dim),
                           CacheTensor("value", self.num_kv_heads, self.value_dim)), self.window)
 
@@ -178,8 +216,12 @@ class SinkAttention(Mixer):
                 if v_other is None:
                     raise ValueError(f"sink_attention: no layer published the values {key!r} before this one")
         q = attn_ops.qkv_rotate_store(qkv, ctx.positions, ctx.seq_of_token, cache, inv_freq, rotary_dim, H, G, dk, dv,
-                                      ctx.dtype, v_other=v_other, blend=self.blend)
+                                      ctx.dtype, v_other=v_other, blend=self.blend, q_norm=self.q_norm,
+                                      k_norm=self.k_norm, norm_eps=self.norm_eps, v_norm=self.value_norm,
+                                      v_inv_freq=self.value_freq)
         out = torch.empty((q.shape[0], H * dv), dtype=q.dtype, device=q.device)
         attn_ops.sink_paged_attention(ctx, q, cache, out, H, G, dk, dv, self.window,
-                                      self.scale * self.position_encoding.score_scale(), self.sink)
+                                      self.scale * self.position_encoding.score_scale(), bool(self.sink),
+                                      chunked=self.mask == "chunk", sink_values=self.sink_values,
+                                      turn_freq=self.value_freq)
         return ops.linear(out, self.w_o, out_dtype=torch.float32)

@@ -13,7 +13,7 @@ import torch
 from dispec_b200.ops.gemm import NormedRows
 from dispec_b200 import ops
 from dispec_b200.ops import norm32 as norm32_ops
-from dispec_b200.parts.base import Block, TensorSpec, WideStream
+from dispec_b200.parts.base import Block, Part, TensorSpec, WideStream
 from dispec_b200.registry import register_part
 
 
@@ -171,3 +171,96 @@ class GatedPreNormBlock(Block):
         nxt = norm32_ops.stream_update(full, y, rms_weight=self.token_input.norm_weight, rms_eps=self.token_input.eps,
                                        norm_weight=nw, norm_eps=ne, out_dtype=ctx.dtype if nw is not None else None)
         return x, nxt
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and a norm after every sublayer, the normed result scaled per channel, on a
+    residual stream kept in 32-bit floats (``WideStream``):
+
+        x <- x + scale1 * out_norm1(mixer(norm1(x)))
+        x <- x + scale2 * out_norm2(ffn(norm2(x)))            (if there is a feed-forward)
+
+    The four norms are RMS norms given as parts with a float32 ``weight`` per coordinate and an
+    ``eps`` (``rms_norm_f32``, ``rms_norm_scalar_f32``).  The sublayers return 32-bit rows.  Each
+    sum runs as one kernel with the norm of the addend before it and the norm that reads the new
+    stream after it (the out-norm's gain and the channel scale are one vector there); the block
+    hands the next block's first norm of its result on as ``pending`` when that block asks for it."""
+
+    def __init__(self, hidden_size: int, mixer_norm, mixer, mixer_out_norm, ffn_norm=None, feed_forward=None,
+                 ffn_out_norm=None):
+        if len({ffn_norm is None, feed_forward is None, ffn_out_norm is None}) != 1:
+            raise ValueError("sandwich_norm: a feed-forward and its two norms come together or not at all")
+        self.hidden_size = hidden_size
+        self.mixer_norm, self.mixer, self.mixer_out_norm = mixer_norm, mixer, mixer_out_norm
+        self.ffn_norm, self.feed_forward, self.ffn_out_norm = ffn_norm, feed_forward, ffn_out_norm
+        self.gain1 = self.gain2 = None
+
+    def tensor_specs(self):
+        specs = {"scale1": TensorSpec((self.hidden_size,), dtype="float32", init="one_plus_normal")}
+        if self.feed_forward is not None:
+            specs["scale2"] = TensorSpec((self.hidden_size,), dtype="float32", init="one_plus_normal")
+        return specs
+
+    def load(self, tensors):
+        self.t = dict(tensors)
+
+    def prepare(self, device):
+        # gain of the norm after the sublayer times the channel scale: what multiplies addend / rms(addend)
+        self.gain1 = (self.mixer_out_norm.weight * self.t["scale1"]).contiguous()
+        if self.feed_forward is not None:
+            self.gain2 = (self.ffn_out_norm.weight * self.t["scale2"]).contiguous()
+
+    def first_norm_after_product(self):
+        return self.mixer_norm.weight, self.mixer_norm.eps
+
+    def forward(self, ctx, x, pending, cache, state, then_norm=None):
+        if not isinstance(x, WideStream) or x.full.dtype != torch.float32:
+            raise ValueError("sandwich_norm: the residual stream must be a 32-bit WideStream")
+        full = x.full
+        h = pending if pending is not None else self.mixer_norm.forward(ctx, x)
+        y, gain, eps = self.mixer.forward(ctx, h, cache, state), self.gain1, self.mixer_out_norm.eps
+        if self.feed_forward is not None:
+            h = norm32_ops.stream_update(full, y, rms_weight=gain, rms_eps=eps, norm_weight=self.ffn_norm.weight,
+                                         norm_eps=self.ffn_norm.eps, norm_kind="rms", out_dtype=ctx.dtype)
+            y, gain, eps = self.feed_forward.forward(ctx, h), self.gain2, self.ffn_out_norm.eps
+        nw, ne = then_norm if then_norm is not None else (None, 0.0)
+        nxt = norm32_ops.stream_update(full, y, rms_weight=gain, rms_eps=eps, norm_weight=nw, norm_eps=ne,
+                                       norm_kind="rms", out_dtype=ctx.dtype if nw is not None else None)
+        return x, nxt
+
+
+@register_part("stream_input", "pass_entry")
+class PassEntry(Part):
+    """What enters a 32-bit residual stream where a pass over a run of repeated layers begins:
+
+        x <- x + x0 + step[t]      (t: the number of the pass; x0, the embedding output, only in
+                                    passes after the first and only with ``reinject``)
+
+    ``step`` is a tensor [times, hidden_size].  One kernel does the sum and, when the layer that
+    follows asks for it, that layer's first norm of the new stream (an RMS norm)."""
+
+    def __init__(self, hidden_size: int, times: int, reinject: bool = True):
+        if times < 1:
+            raise ValueError(f"pass_entry: times={times} must be at least 1")
+        self.hidden_size, self.times, self.reinject = hidden_size, int(times), bool(reinject)
+
+    @property
+    def needs_embedding(self) -> bool:
+        return self.reinject and self.times > 1
+
+    def tensor_specs(self):
+        return {"step": TensorSpec((self.times, self.hidden_size), dtype="float32")}
+
+    def load(self, tensors):
+        self.step = tensors["step"]
+
+    def forward(self, ctx, x, x0, t: int, then_norm=None):
+        if not isinstance(x, WideStream) or x.full.dtype != torch.float32:
+            raise ValueError("pass_entry: the residual stream must be a 32-bit WideStream")
+        if not 0 <= t < self.times:
+            raise ValueError(f"pass_entry: pass {t} of {self.times}")
+        nw, ne = then_norm if then_norm is not None else (None, 0.0)
+        y = x0 if (self.reinject and t > 0) else None
+        return norm32_ops.stream_update(x.full, y, bias=self.step[t], norm_weight=nw, norm_eps=ne, norm_kind="rms",
+                                        out_dtype=ctx.dtype if nw is not None else None)

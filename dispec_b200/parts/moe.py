@@ -1,4 +1,8 @@
-"""Mixture-of-experts feed-forward with grouped routing.
+"""Mixture-of-experts feed-forwards: ``grouped_moe`` (below) and ``glu_moe`` (experts that are
+clamped gated units, sigmoid or softmax scores, the weight on the expert's input or output, an
+optional shared expert; at the end of this file).
+
+``grouped_moe``:
 
 Scores s = softmax(W_router h) over all experts, in 32-bit (the router matrix stays float32 in
 every mode).  The experts form ``num_groups`` equal runs of neighbours; a group's score is its
@@ -50,3 +54,68 @@ class GroupedMoE(FeedForward):
         a = moe_ops.expert_product(plan, x, self.w_up, x.dtype, rows_are_tokens=True, scatter=False, square_relu=True)
         y = moe_ops.expert_product(plan, a, self.w_down, torch.float32, rows_are_tokens=False, scatter=True)
         return moe_ops.combine(y, wts, ids)
+
+
+@register_part("feed_forward", "glu_moe")
+class GatedMoE(FeedForward):
+    """Mixture of experts whose experts are clamped gated units without biases:
+
+        expert_e(a) = W_down_e y,  y = g * sigmoid(alpha * g) * (u + 1),
+        g = min(W_gate_e a, limit),  u = clamp(W_up_e a, -limit, limit).
+
+    Router logits z = W_router h in 32-bit (the router matrix stays float32 in every mode);
+    scores s = sigmoid(z) (``score`` "sigmoid") or softmax(z); groups of experts as in
+    ``grouped_moe``; the ``top`` largest scores name the token's experts and are their weights w,
+    not renormalised.  ``weight_on`` "input": the output is the sum of expert_e(w h) (the factor is
+    applied to the 32-bit sums W_gate_e h and W_up_e h, which is the same product, before the
+    clamps); "output": the sum of w expert_e(h).  ``shared``: a feed-forward part that runs for
+    every token and is added.  Everything runs on the device (``ops.moe``)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, limit: float,
+                 alpha: float = 1.702, score: str = "sigmoid", weight_on: str = "input", num_groups: int = 1,
+                 keep_groups: int = 1, shared=None):
+        if num_experts <= 0 or num_groups <= 0 or num_experts % num_groups:
+            raise ValueError(f"glu_moe: {num_experts} experts do not form {num_groups} equal groups")
+        if not 0 < keep_groups <= num_groups:
+            raise ValueError(f"glu_moe: keep_groups={keep_groups} outside 1..{num_groups}")
+        if not 0 < top <= keep_groups * (num_experts // num_groups):
+            raise ValueError(f"glu_moe: top={top} experts cannot come from {keep_groups} groups of "
+                             f"{num_experts // num_groups}")
+        if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
+            raise ValueError(f"glu_moe: score={score!r} / weight_on={weight_on!r} are not known")
+        if not limit > 0:
+            raise ValueError(f"glu_moe: the limit must be positive, got {limit}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top, self.num_groups, self.keep_groups = num_experts, top, num_groups, keep_groups
+        self.limit, self.alpha, self.score, self.weight_on = float(limit), float(alpha), score, weight_on
+        self.shared = shared
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        specs = {"router.weight": TensorSpec((self.num_experts, h), dtype="float32")}
+        for e in range(self.num_experts):
+            specs[f"experts.{e}.gate.weight"] = TensorSpec((i, h))
+            specs[f"experts.{e}.up.weight"] = TensorSpec((i, h))
+            specs[f"experts.{e}.down.weight"] = TensorSpec((h, i))
+        return specs
+
+    def load(self, tensors):
+        E, h, i = self.num_experts, self.hidden_size, self.intermediate_size
+        self.w_router = tensors["router.weight"]
+        # rows of the gate and up matrices in turn: the product's epilogue holds a gate and its up
+        # value in one thread and writes the unit's result
+        self.w_gate_up = torch.stack(
+            [torch.stack([tensors[f"experts.{e}.gate.weight"], tensors[f"experts.{e}.up.weight"]], dim=1).reshape(2 * i, h)
+             for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[f"experts.{e}.down.weight"] for e in range(E)]).contiguous()
+
+    def forward(self, ctx, x):
+        ids, wts = moe_ops.route(x, self.w_router, self.num_groups, self.keep_groups, self.top, score=self.score)
+        plan = moe_ops.plan(ids, self.num_experts, moe_ops.tensor_cores_supported(x.dtype, self.hidden_size,
+                                                                                   self.intermediate_size))
+        on_input = self.weight_on == "input"
+        a = moe_ops.expert_product(plan, x, self.w_gate_up, x.dtype, rows_are_tokens=True, scatter=False,
+                                   clamped_glu=(self.limit, self.alpha), row_scale=wts.view(-1) if on_input else None)
+        y = moe_ops.expert_product(plan, a, self.w_down, torch.float32, rows_are_tokens=False, scatter=True)
+        base = self.shared.forward(ctx, x) if self.shared is not None else None
+        return moe_ops.combine(y, None if on_input else wts, ids, base=base)

@@ -81,6 +81,19 @@ class RMSNorm32(Norm):
         return WideStream(full, rounded)
 
 
+@register_part("norm", "rms_norm_scalar_f32")
+class ScalarRMSNorm32(RMSNorm32):
+    """y = g * x / sqrt(mean(x^2) + eps) with one number g for all coordinates (a tensor without
+    dimensions), everything in 32-bit.  The kernels take a gain per coordinate: ``weight`` is g
+    repeated ``hidden_size`` times."""
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((), dtype="float32", init="one_plus_normal")}
+
+    def load(self, tensors):
+        self.weight = tensors["weight"].reshape(1).expand(self.hidden_size).contiguous()
+
+
 @register_part("norm", "layer_norm_f32")
 class LayerNorm32(Norm):
     """y = (x - mean) / sqrt(var + eps) * w with a gain and no bias (var: the mean of the squared

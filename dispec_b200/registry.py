@@ -31,7 +31,7 @@ class ArchitectureEntry:
 _ARCHITECTURES: dict[str, ArchitectureEntry] = {}
 _PARTS: dict[str, dict[str, type]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {},
-    "embedding": {}, "head": {},
+    "embedding": {}, "head": {}, "stream_input": {},
 }
 
 

@@ -741,6 +741,129 @@ def murutar_points(args, pk: dict) -> dict:
             print(f"bench: {key} done", file=sys.stderr, flush=True)
     return out
 
+# ------------------------------------------------------------ Desalix beside Murutar at equal size
+# Desalix's closest relative in this package is Murutar (attention with a sink over a bounded span
+# of keys, clamped gated units, experts, a 32-bit residual stream).  Both with attention + experts
+# in every layer, at the same width, heads, key and value sizes, span (a chunk of 1,024 positions
+# against a window of 1,024 keys), vocabulary, number of experts and feed-forward weights a token
+# passes.  Desalix: eight layers of which the third and fourth are passed twice (ten layer runs);
+# 16 experts of a quarter of the dense width of which 2 are used, and a shared expert of half of it.
+# Murutar: ten layers, 16 experts of half the dense width of which 2 are used.
+DESALIX_LAYERS, DESALIX_LOOP = 8, (2, 4, 2)
+
+
+def desalix_config(shape: str) -> dict:
+    z = MURUTAR_SHAPES[shape]
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["ff"] // 2, "limit": 7.0}}
+    layer = {"type": "attention", "mlp": mlp,
+             "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                       "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["rot"]}, "scale": z["dim"] ** -0.5}}
+    return {"architecture": "Desalix", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": [layer] * DESALIX_LAYERS,
+            "loop": dict(zip(("start", "stop", "times"), DESALIX_LOOP))}
+
+
+def murutar_attention_experts_config(shape: str, layers: int) -> dict:
+    z = MURUTAR_SHAPES[shape]
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    layer = {"type": "attention", "mlp": moe,
+             "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                       "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["rot"]}, "scale": z["dim"] ** -0.5}}
+    return {"architecture": "Murutar", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": z["width"] ** 0.5},
+            "norm": {"eps": 1e-6}, "layers": [layer] * layers}
+
+
+def desalix_bytes_and_flops(cfg: dict):
+    """As ``murutar_bytes_and_flops``, per layer run: a layer that is passed twice is read twice (its
+    weights do not stay in the L2 between the passes at these sizes) and has two caches."""
+    W, V = cfg["width"], cfg["vocab"]
+    loop = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    runs = [1 + (loop["times"] - 1) * (loop["start"] <= i < loop["stop"]) for i in range(len(cfg["layers"]))]
+    fixed = unique = 0
+    cache_layers, attn, expert_layers = [], [], []
+    for e, n_runs in zip(cfg["layers"], runs):
+        m, mlp = e["mixer"], e["mlp"]
+        H, G, d, dv, size = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+        n = (H * d + G * d + G * dv) * W + W * H * dv + 2 * mlp["router"]["experts"] * W  # float32 router
+        n += 3 * mlp["shared"]["ff"] * W
+        one = 3 * mlp["expert"]["ff"] * W
+        fixed += n * n_runs
+        unique += n + mlp["router"]["experts"] * one
+        for _ in range(n_runs):
+            cache_layers.append((G * (d + dv) * 2, size))
+            attn.append((H * (d + dv), size))
+            expert_layers.append((mlp["router"]["experts"], mlp["router"]["top"], one))
+
+    def weight_bytes(batch):
+        return 2 * (fixed + V * W + sum(min(E, batch * top) * w for E, top, w in expert_layers))
+
+    def cache_bytes(ctx):  # the keys of the current chunk: on average half a chunk, here what the context leaves of it
+        return sum(per * ((ctx % size) + 1 if size else ctx) for per, size in cache_layers)
+
+    def prefill_flops(T):
+        f = 2 * T * (fixed + sum(top * w for _, top, w in expert_layers)) + 2 * V * W
+        for per, size in attn:
+            keys = sum((t % size) + 1 if size else t + 1 for t in range(T))
+            f += 2 * per * keys
+        return f
+
+    return weight_bytes, cache_bytes, 0, prefill_flops, 2 * (unique + 2 * V * W)
+
+
+def desalix_points(args, pk: dict) -> dict:
+    """Prefill (2,048 tokens in one step) and decode (batch 1, 8, 64 from captured graphs) of Desalix
+    and of Murutar with attention and experts in every layer, at equal sizes and equally many layer
+    runs, each with the fraction of its own roofline.  Decoding starts 1,536 tokens into the
+    sequence, so that Desalix's chunk holds about 512 keys (the mean over a chunk) while Murutar's
+    window holds its 1,024."""
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner
+    from dispec_b200.weights import load_random_model
+    prompt_len = PROMPT_LEN + PROMPT_LEN // 2
+    out = {"only": "desalix", "layers": DESALIX_LAYERS, "loop": DESALIX_LOOP, "prompt_len": prompt_len,
+           "prefill_tokens": PREFILL_TOKENS, "peaks": pk}
+    steps, warmup = max(20, min(args.steps, 50)), max(3, args.warmup // 2)
+    per_req = (prompt_len + NEW_TOKENS + steps + warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    shapes = ["1.5b"] if args.no_other_shapes else list(MURUTAR_SHAPES)
+    runs = DESALIX_LAYERS + (DESALIX_LOOP[1] - DESALIX_LOOP[0]) * (DESALIX_LOOP[2] - 1)
+    for shape in shapes:
+        for family in ("desalix", "murutar"):
+            if family == "desalix":
+                cfg_dict = desalix_config(shape)
+                weight_bytes, cache_bytes, state_bytes, prefill_flops, total = desalix_bytes_and_flops(cfg_dict)
+            else:
+                cfg_dict = murutar_attention_experts_config(shape, runs)
+                weight_bytes, cache_bytes, state_bytes, prefill_flops, total = murutar_bytes_and_flops(cfg_dict)
+            vocab = cfg_dict["vocab"]
+            model = load_random_model(load_model_config(cfg_dict), 5, STD, "bfloat16", "cuda:0")
+            torch.cuda.synchronize()
+            key = f"{family}_{shape}"
+            out[f"{key}_weight_gb"] = round(total / 1e9, 3)
+            for b in (1, 8, 64):
+                r = ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(b * per_req, 160), max_num_seqs=max(b, 8),
+                                cuda_graph=True)
+                ms, launches, ctx = decode_direct(r, random_prompts(b, prompt_len, vocab, 13 + b), steps, warmup)
+                step_bytes = weight_bytes(b) + b * (cache_bytes(ctx) + state_bytes)
+                out[f"{key}_decode_b{b}"] = round(b * 1000.0 / ms, 1)
+                out[f"{key}_decode_b{b}_ms"] = round(ms, 4)
+                out[f"{key}_decode_b{b}_hbm_frac"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                out[f"{key}_decode_b{b}_launches_per_step"] = launches // steps
+                print(f"bench: {key} decode at batch {b}: {ms:.3f} ms a step", file=sys.stderr, flush=True)
+                if b == 1:
+                    pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=3)
+                    out[f"{key}_prefill"] = round(PREFILL_TOKENS / pms * 1000.0, 1)
+                    out[f"{key}_prefill_ms"] = round(pms, 3)
+                    out[f"{key}_prefill_frac"] = round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+                del r
+                torch.cuda.empty_cache()
+            del model
+            torch.cuda.empty_cache()
+            print(f"bench: {key} done", file=sys.stderr, flush=True)
+    return out
+
 
 def run_ours(args) -> dict:
     import torch
@@ -760,6 +883,8 @@ def run_ours(args) -> dict:
         return puludra_points(args, peaks())
     if args.only == "murutar":
         return murutar_points(args, peaks())
+    if args.only == "desalix":
+        return desalix_points(args, peaks())
     cfg_dict = dict(BENCH_CONFIG)
     seed = SEED
     if args.shape != "1.5b":
@@ -929,14 +1054,16 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra", "murutar"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra", "murutar", "desalix"],
+                    default=None,
                     help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
                          "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
                          "tcgen05.mma for one to four issuing threads; tma-rate: bytes a clock an SM takes in from "
                          "the L2 by TMA, by the size of a request; attn-prefill: the attention kernel for portions of prompts "
                          "alone, by shape, length and the order of the pages; puludra: prefill and decode of the Puludra design beside "
                          "Qwen2 at equal width, depth, vocabulary and feed-forward width (eight layers each), with roofline fractions; "
-                         "murutar: the same for the Murutar design beside Puludra")
+                         "murutar: the same for the Murutar design beside Puludra; desalix: the same for the Desalix design beside "
+                         "Murutar with attention and experts in every layer")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")

@@ -68,7 +68,8 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [BM][LDK]
   bf16* Ks = Qs + BM * LDK;                      // [2][BN][LDK]
   bf16* Vs = Ks + 2 * BN * LDK;                  // [2][BN][LDV]
-  const int tile = blockIdx.x + tile_offset, g = blockIdx.y, split = blockIdx.z;
+  // the last tiles of a prompt have the most keys: they start first, so that short ones fill the tail
+  const int tile = (int)(gridDim.x - 1 - blockIdx.x) + tile_offset, g = blockIdx.y, split = blockIdx.z;
   const int seq = tile_seq[tile], tok0 = tile_tok0[tile];
   const int qs = q_start[seq], qlen = q_start[seq + 1] - qs, clen = ctx_len[seq];
   if (clen <= 0 || tok0 >= qlen) return;

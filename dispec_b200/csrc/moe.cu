@@ -57,7 +57,7 @@ __device__ __forceinline__ Best warp_best(Best b) {
   return b;
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float* __restrict__ w, int T, int W, int E,
                  int groups, int keep, int top, int score_kind, int* __restrict__ ids, float* __restrict__ wts) {
   extern __shared__ float sm[];
@@ -75,6 +75,7 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
     const float* we = w + (size_t)e * W;
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     int i = lane;
+#pragma unroll 4
     for (; i + 96 < W; i += 128) {
       a0 = fmaf(we[i], hs[i], a0);
       a1 = fmaf(we[i + 32], hs[i + 32], a1);
@@ -403,7 +404,10 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
               "dsp_moe_route: experts=%d groups=%d keep=%d top=%d do not fit together", E, groups, keep, top);
   const size_t smem = (size_t)(2 * E + groups + W) * sizeof(float);
   DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts over a width of %d are more than the router kernel holds", E, W);
-  DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)T), dim3(128), smem, stream, h, h_dtype, ldh, w, T, W, E,
+  // a warp an expert where the block can hold them: the logits are chains of dependent rounds of loads,
+  // and a step of a few tokens waits for the longest chain (the sums do not depend on the block's shape)
+  const unsigned threads = 32u * (unsigned)min(max(E, 4), 32);
+  DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)T), dim3(threads), smem, stream, h, h_dtype, ldh, w, T, W, E,
                         groups, keep, top, score_kind, ids, wts));
   DSP_CHECK_LAUNCH("dsp_moe_route");
   return 0;

@@ -180,6 +180,9 @@ def build_desalix(cfg: DesalixConfig) -> ModelSpec:
     h = cfg.hidden_size
     norm = lambda name: PartSpec("norm", "rms_norm_scalar_f32", {"hidden_size": h, "eps": cfg.eps}, {"weight": name})
     blocks = []
+    # a checkpoint may carry the stream norms and channel scale of a feed-forward that a layer does
+    # not have, and the pass vectors of a run that is empty: they are ignored
+    spare = set() if cfg.loop_times else {"loop.step"}
     for i, e in enumerate(cfg.layers):
         p = f"l{i}."
         params = {"hidden_size": h, "mixer_norm": norm(p + "norm1"), "mixer": _mixer_spec(cfg, e["mixer"], p + "mix."),
@@ -189,6 +192,8 @@ def build_desalix(cfg: DesalixConfig) -> ModelSpec:
             params.update(ffn_norm=norm(p + "norm2"), feed_forward=_ffn_spec(cfg, e["mlp"], p + "mlp."),
                           ffn_out_norm=norm(p + "norm2b"))
             tensors["scale2"] = p + "ls2"
+        else:
+            spare.update({p + "norm2", p + "norm2b", p + "ls2"})
         blocks.append(PartSpec("block", "sandwich_norm", params, tensors))
     # every run of a layer has a cache of its own (its label is its place in the schedule)
     schedule = [LayerCall(layer, None, True, entry) for layer, entry in cfg.layer_runs()]
@@ -203,7 +208,8 @@ def build_desalix(cfg: DesalixConfig) -> ModelSpec:
                            {"weight": "embed"}),
         layers=blocks, final_norm=norm("final.norm"),
         head=PartSpec("head", "linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": h}, {"weight": "head"}),
-        schedule=schedule, pass_entry=pass_entry, vocab_size=cfg.vocab_size, max_position=cfg.max_position_embeddings)
+        schedule=schedule, pass_entry=pass_entry, vocab_size=cfg.vocab_size, max_position=cfg.max_position_embeddings,
+        optional_tensors=frozenset(spare))
 
 
 register_architecture(DesalixConfig.architecture, DesalixConfig, build_desalix)

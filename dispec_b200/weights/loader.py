@@ -57,7 +57,10 @@ def check_source(model: DecoderModel, source, where: str) -> dict:
     for n, spec in req.items():
         if n not in have:
             continue
-        if tuple(source.shape(n)) != tuple(spec.shape):
+        got = tuple(source.shape(n))
+        # a single number may be stored without dimensions or as one element of any rank
+        scalar = not tuple(spec.shape) and all(d == 1 for d in got)
+        if got != tuple(spec.shape) and not scalar:
             wrong_shape.append((n, tuple(source.shape(n)), tuple(spec.shape)))
         is_float = source.dtype(n).is_floating_point
         if spec.dtype == "int32" and is_float:
@@ -77,6 +80,8 @@ def load_into(model: DecoderModel, source, dtype, device, where: str = "weights"
     tensors = {}
     for name, spec in req.items():
         t = source.get(name)
+        if not tuple(spec.shape):
+            t = t.reshape(())
         if spec.dtype == "model":
             target = dtype
         elif spec.dtype == "float32":

@@ -62,6 +62,33 @@ def test_an_empty_or_missing_loop_repeats_nothing():
                                                                   (0, 1), (1, None), (2, None), (3, None)]
 
 
+def test_tensors_of_pieces_a_model_lacks_may_be_present():
+    c = copy.deepcopy(du.CONFIGS["mix"]["config"])  # its third layer has no feed-forward
+    _, m = build(c)
+    assert m.spec.optional_tensors == {"l2.norm2", "l2.norm2b", "l2.ls2"}
+    c["loop"] = {"start": 2, "stop": 2, "times": 5}
+    assert "loop.step" in build(c)[1].spec.optional_tensors
+
+
+def test_a_single_number_may_be_stored_with_dimensions():
+    from dispec_b200.weights.loader import check_source
+
+    config = du.CONFIGS["flat"]["config"]
+    _, m = build(config)
+    shapes = du.tensor_shapes(config)
+    shapes["final.norm"], shapes["l0.norm1"] = (1,), (1, 1)
+
+    class Source:
+        names = lambda self: list(shapes)
+        shape = lambda self, n: shapes[n]
+        dtype = lambda self, n: torch.bfloat16
+
+    check_source(m, Source(), "test")
+    shapes["l1.norm2b"] = (2,)
+    with pytest.raises(Exception, match="l1.norm2b"):
+        check_source(m, Source(), "test")
+
+
 @pytest.mark.parametrize("change,word", [
     (lambda c: c["layers"][0].update(type="conv"), "not implemented"),
     (lambda c: c["layers"][0]["mixer"].pop("vdim"), "vdim"),

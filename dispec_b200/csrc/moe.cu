@@ -95,34 +95,36 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
   for (int e = lane; e < E; e += 32) sum += expf(sc[e] - mx);
   sum = warp_sum(sum);
   __syncwarp();
+  // sigmoid scores are chosen by their logits: the order is the same, and two logits whose sigmoids
+  // both round to 1 still differ
   for (int e = lane; e < E; e += 32) {
-    sc[e] = score_kind == 1 ? 1.f / (1.f + expf(-sc[e])) : expf(sc[e] - mx) / sum;
+    if (score_kind != 1) sc[e] = expf(sc[e] - mx) / sum;
     ok[e] = 0.f;
   }
   __syncwarp();
   const int per = E / groups;
   for (int g = lane; g < groups; g += 32) {
-    float b = -1.f;
+    float b = -INFINITY;
     for (int j = 0; j < per; ++j) b = fmaxf(b, sc[g * per + j]);
     gb[g] = b;
   }
   __syncwarp();
   for (int r = 0; r < keep; ++r) {
-    Best b = {-1.f, -1};
-    for (int g = lane; g < groups; g += 32) b = better(b, Best{gb[g], gb[g] >= 0.f ? g : -1});
+    Best b = {-INFINITY, -1};
+    for (int g = lane; g < groups; g += 32) b = better(b, Best{gb[g], gb[g] > -INFINITY ? g : -1});
     b = warp_best(b);
     if (b.i < 0) break;
     for (int j = lane; j < per; j += 32) ok[b.i * per + j] = 1.f;
-    if (lane == 0) gb[b.i] = -1.f;
+    if (lane == 0) gb[b.i] = -INFINITY;
     __syncwarp();
   }
   for (int r = 0; r < top; ++r) {
-    Best b = {-1.f, -1};
+    Best b = {-INFINITY, -1};
     for (int e = lane; e < E; e += 32) b = better(b, Best{sc[e], ok[e] > 0.f ? e : -1});
     b = warp_best(b);
     if (lane == 0) {
       ids[t * top + r] = b.i;
-      wts[t * top + r] = b.i >= 0 ? b.v : 0.f;
+      wts[t * top + r] = b.i < 0 ? 0.f : score_kind == 1 ? 1.f / (1.f + expf(-b.v)) : b.v;
       if (b.i >= 0) ok[b.i] = 0.f;
     }
     __syncwarp();

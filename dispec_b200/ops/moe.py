@@ -16,7 +16,8 @@ def _lib():
 def route(h: torch.Tensor, w_router: torch.Tensor, groups: int, keep: int, top: int, score: str = "softmax"):
     """h [T, W] (either type), w_router float32 [E, W] -> (ids int32 [T, top], weights float32
     [T, top]): softmax over all experts in 32-bit (``score`` "sigmoid": the sigmoid of every
-    expert's logit instead); the ``top`` largest scores among the experts
+    expert's logit instead, chosen by the logits, so that scores which round to the same number
+    do not tie); the ``top`` largest scores among the experts
     of the ``keep`` groups (of ``groups`` equal runs of neighbours) with the largest best score;
     the weights are those scores."""
     if not (h.is_cuda and w_router.is_cuda):

@@ -319,6 +319,23 @@ def test_router_kernel_with_sigmoid_scores(E, top):
         assert (wts[t].cpu().double() - s[got]).abs().max() < 1e-6
 
 
+def test_router_kernel_tells_apart_logits_whose_sigmoids_round_to_one():
+    """Logits of 18 to 40 all have a 32-bit sigmoid of exactly 1: the largest logits are chosen all the
+    same, not the first experts among the equal scores; very negative ones (scores near 0) likewise."""
+    from dispec_b200.ops import moe
+    E, W = 7, 16
+    w = torch.zeros(E, W)
+    h = torch.zeros(3, W)
+    h[:, 0] = 1.0
+    w[:, 0] = torch.tensor([18.0, 30.0, 22.0, 40.0, 19.0, 35.0, 21.0])
+    h[1, 0] = -1.0  # logits -18 ... -40: the largest are experts 0, 4, 6
+    h[2, 0] = 0.0   # all logits 0: the first experts win the ties
+    ids, wts = moe.route(dev(h), dev(w), 1, 1, 3, score="sigmoid")
+    assert sorted(ids[0].tolist()) == [1, 3, 5] and (wts[0] == 1.0).all()
+    assert sorted(ids[1].tolist()) == [0, 4, 6] and (wts[1] < 1e-7).all() and (wts[1] > 0).all()
+    assert sorted(ids[2].tolist()) == [0, 1, 2] and (wts[2] == 0.5).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,W,ff,E,top,shared,weight_on", [
     (1, 20, 6, 4, 1, None, "input"), (45, 52, 14, 9, 4, (10, 0.7), "input"), (150, 64, 40, 6, 2, (24, 1.5), "input"),

@@ -63,6 +63,13 @@ CONFIGS = {
         attention(4, 2, 8, 12, chunk=24, rot=8, mlp=moe(4, 2, 32, shared=(24, 1.0))),
         attention(4, 4, 12, 8, chunk=5, turn=False, mlp=moe(2, 1, 16)),
     ]), seed=34, page_size=16),
+    # chunks of hundreds of positions (many pages and key tiles; single tokens' keys cut into shares),
+    # one of them no multiple of a page, a layer that sees everything; sizes the tensor-core kernels take
+    "long": dict(config=model(128, 200, [
+        attention(4, 2, 32, 32, chunk=512, rot=16, mlp=moe(4, 2, 32, shared=(32, 1.0))),
+        attention(6, 1, 16, 48, chunk=300, rot=16, base=1e5, scale=0.3, mlp=moe(3, 1, 48, limit=2.0)),
+        attention(2, 2, 64, 16, rot=32, base=500.0, mlp=None),
+    ], loop=(0, 2, 2)), seed=36, page_size=16),
     # every layer runs four times
     "all_looped": dict(config=model(40, 70, [attention(2, 1, 16, 16, chunk=16, rot=16, mlp=moe(3, 1, 24))],
                                     loop=(0, 1, 4)), seed=35, page_size=16),

@@ -21,7 +21,7 @@ import replay_util as ru
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"mix": [1, 9, 40, 131, 260], "odd": [2, 17, 64, 150], "wide": [3, 33, 97, 230],
-           "flat": [1, 23, 24, 25, 70], "all_looped": [1, 2, 45, 100]}
+           "flat": [1, 23, 24, 25, 70], "all_looped": [1, 2, 45, 100], "long": [4, 299, 340, 705]}
 LENGTHS.update({k + suffix: v for k, v in LENGTHS.items() for suffix in ("_one_expert", "_every_expert")})
 
 CLOSE_CALL = 0.02  # difference of router scores below which bfloat16 activations may route a token otherwise
@@ -105,7 +105,7 @@ def with_every_expert_chosen(name):
     return name + "_every_expert"
 
 
-@pytest.mark.parametrize("name", ["mix", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mix", "odd", "wide", "long"])
 @pytest.mark.parametrize("variant", [with_one_expert, with_every_expert_chosen])
 def test_replay_bfloat16_without_routing_is_within_rounding_everywhere(name, variant, tmp_path):
     assert replay(variant(name), "bfloat16", tmp_path) == 1.0
@@ -116,7 +116,7 @@ def test_replay_bfloat16_single_token_steps_from_captured_graphs(name, tmp_path)
     replay(name, "bfloat16", tmp_path, cuda_graph=True)
 
 
-@pytest.mark.parametrize("name", ["mix", "odd", "flat", "all_looped"])
+@pytest.mark.parametrize("name", ["mix", "odd", "flat", "all_looped", "long"])
 def test_replay_float32_sharp_chunk_edges_and_far_keys(name, tmp_path):
     replay(name, "float32", tmp_path, sharp=True)
 

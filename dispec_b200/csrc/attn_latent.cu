@@ -13,8 +13,12 @@
 //
 // latent_store_kernel: RMS norm (32-bit) of the first R columns of the down projection with a
 // gain, rotation of the last r columns, both written to the token's place in the pages.
-// The rotation turns the pairs (2i, 2i+1) of the first `rot` of the r dimensions by the angle
-// position * inv_freq[i] (interleaved layout); the rest pass unchanged.
+// The rotation turns pair i of the first `rot` of the r dimensions by the angle
+// position * inv_freq[i]; the rest pass unchanged.  `layout` 0: pair i = (2i, 2i+1) (interleaved);
+// 1: pair i = (i, i + rot/2) (halves).  Cosine and sine are multiplied by `mag` (a rotation that also
+// stretches: both the query's and the key's part are, so their product carries mag^2).
+// `window` W > 0: the query at position p sees the keys j with p - W < j <= p (0: every j <= p);
+// older keys are never looked up, their pages may have been given back.
 //
 // pools: latent [num_pages, 1, page_size, R], rotated key [num_pages, 1, page_size, r];
 // page = page_table[seq * pt_stride + position / page_size].
@@ -24,10 +28,22 @@ namespace {
 constexpr int THREADS = 128;  // = keys per tile
 constexpr int GCHUNK = 8;     // heads per block
 
+// Element j (< rot) of a vector that is turned: which frequency, which element is its partner, and
+// whether j is the second of the pair (u, v) -> (u c - v s, v c + u s).
+struct PairOf {
+  int freq, other;
+  bool second;
+};
+__device__ __forceinline__ PairOf pair_of(int j, int rot, int layout) {
+  if (layout == 0) return PairOf{j >> 1, j ^ 1, (j & 1) != 0};
+  const int half = rot >> 1;
+  return j < half ? PairOf{j, j + half, false} : PairOf{j - half, j - half, true};
+}
+
 __global__ void __launch_bounds__(THREADS)
 latent_store_kernel(const void* __restrict__ down, int d_dtype, long ldd, int c_off, int r_off,
                     const float* __restrict__ gain, float eps, const float* __restrict__ inv_freq,
-                    int rot, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                    int rot, int layout, float mag, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                     const int* __restrict__ page_table, int pt_stride, void* __restrict__ c_pool,
                     void* __restrict__ r_pool, int pool_dtype, int R, int r, int page_size,
                     int num_pages, int* err) {
@@ -53,10 +69,13 @@ latent_store_kernel(const void* __restrict__ down, int d_dtype, long ldd, int c_
   for (int i = threadIdx.x; i < r; i += THREADS) {
     float v = ld_any(down, d_dtype, row + r_off + i);
     if (i < rot) {
+      const PairOf pr = pair_of(i, rot, layout);
       float sn, cs;
-      sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
-      const float other = ld_any(down, d_dtype, row + r_off + (i ^ 1));
-      v = (i & 1) ? v * cs + other * sn : v * cs - other * sn;
+      sincosf((float)pos * inv_freq[pr.freq], &sn, &cs);
+      sn *= mag;
+      cs *= mag;
+      const float other = ld_any(down, d_dtype, row + r_off + pr.other);
+      v = pr.second ? v * cs + other * sn : v * cs - other * sn;
     }
     st_any(r_pool, pool_dtype, place * r + i, v);
   }
@@ -68,7 +87,7 @@ template <typename T, int DPT>
 __global__ void __launch_bounds__(THREADS)
 attn_latent_kernel(const float* __restrict__ qa, long ldqa, const void* __restrict__ q, int q_dtype,
                    long ldq, int q_head_stride, int qr_off, const float* __restrict__ inv_freq, int rot,
-                   const T* __restrict__ c_pool, const T* __restrict__ r_pool,
+                   int layout, float mag, int window, const T* __restrict__ c_pool, const T* __restrict__ r_pool,
                    const int* __restrict__ page_table, int pt_stride, const int* __restrict__ positions,
                    const int* __restrict__ seq_of_token, void* __restrict__ out, int out_dtype, long ldo,
                    int H, int R, int r, int page_size, int num_pages, float scale, int* err) {
@@ -95,10 +114,13 @@ attn_latent_kernel(const float* __restrict__ qa, long ldqa, const void* __restri
       const size_t at = (size_t)t * ldq + (size_t)(h0 + g) * q_head_stride + qr_off;
       v = ld_any(q, q_dtype, at + j);
       if (j < rot) {
+        const PairOf pr = pair_of(j, rot, layout);
         float sn, cs;
-        sincosf((float)pos * inv_freq[j >> 1], &sn, &cs);
-        const float other = ld_any(q, q_dtype, at + (j ^ 1));
-        v = (j & 1) ? v * cs + other * sn : v * cs - other * sn;
+        sincosf((float)pos * inv_freq[pr.freq], &sn, &cs);
+        sn *= mag;
+        cs *= mag;
+        const float other = ld_any(q, q_dtype, at + pr.other);
+        v = pr.second ? v * cs + other * sn : v * cs - other * sn;
       }
     }
     qs[i] = v * scale;
@@ -113,7 +135,7 @@ attn_latent_kernel(const float* __restrict__ qa, long ldqa, const void* __restri
   }
   __syncthreads();
 
-  for (int kt = 0; kt <= pos; kt += THREADS) {
+  for (int kt = window > 0 ? max(0, pos - window + 1) : 0; kt <= pos; kt += THREADS) {
     const int key = kt + tid;
     float s[GCHUNK];
 #pragma unroll
@@ -210,8 +232,8 @@ attn_latent_kernel(const float* __restrict__ qa, long ldqa, const void* __restri
 
 template <typename T, int DPT>
 int launch_attn(const float* qa, long ldqa, const void* q, int q_dtype, long ldq, int q_head_stride,
-                int qr_off, const float* inv_freq, int rot, const void* c_pool, const void* r_pool,
-                const int* page_table, int pt_stride, const int* positions, const int* seq_of_token,
+                int qr_off, const float* inv_freq, int rot, int layout, float mag, int window, const void* c_pool,
+                const void* r_pool, const int* page_table, int pt_stride, const int* positions, const int* seq_of_token,
                 void* out, int out_dtype, long ldo, int T_, int H, int R, int r, int page_size,
                 int num_pages, float scale, int* err, cudaStream_t stream) {
   const size_t smem = (size_t)(GCHUNK * (R + r) + GCHUNK * THREADS) * sizeof(float) + THREADS * sizeof(long);
@@ -222,7 +244,7 @@ int launch_attn(const float* qa, long ldqa, const void* q, int q_dtype, long ldq
   }
   dim3 grid(T_, (H + GCHUNK - 1) / GCHUNK);
   DSP_CUDA(launch_plain(attn_latent_kernel<T, DPT>, grid, dim3(THREADS), smem, stream, qa, ldqa, q, q_dtype,
-                      ldq, q_head_stride, qr_off, inv_freq, rot, (const T*)c_pool, (const T*)r_pool,
+                      ldq, q_head_stride, qr_off, inv_freq, rot, layout, mag, window, (const T*)c_pool, (const T*)r_pool,
                       page_table, pt_stride, positions, seq_of_token, out, out_dtype, ldo, H, R, r,
                       page_size, num_pages, scale, err));
   DSP_CHECK_LAUNCH("dsp_attn_latent");
@@ -231,8 +253,8 @@ int launch_attn(const float* qa, long ldqa, const void* q, int q_dtype, long ldq
 }  // namespace
 
 extern "C" int dsp_latent_store(const void* down, int d_dtype, long ldd, int c_off, int r_off,
-                                const float* gain, float eps, const float* inv_freq, int rot,
-                                const int* positions, const int* seq_of_token, const int* page_table,
+                                const float* gain, float eps, const float* inv_freq, int rot, int layout,
+                                float mag, const int* positions, const int* seq_of_token, const int* page_table,
                                 int pt_stride, void* c_pool, void* r_pool, int pool_dtype, int T_, int R,
                                 int r, int page_size, int num_pages, cudaStream_t stream) {
   if (T_ == 0) return 0;
@@ -240,16 +262,17 @@ extern "C" int dsp_latent_store(const void* down, int d_dtype, long ldd, int c_o
   DSP_REQUIRE(err != nullptr, "dsp_latent_store: no device error word");
   DSP_REQUIRE(down && gain && c_pool && r_pool && R > 0 && r >= 0, "dsp_latent_store: missing operand");
   DSP_REQUIRE(rot >= 0 && rot <= r && rot % 2 == 0 && (rot == 0 || inv_freq), "dsp_latent_store: rot=%d of %d", rot, r);
+  DSP_REQUIRE(layout == 0 || layout == 1, "dsp_latent_store: unknown layout %d", layout);
   DSP_CUDA(launch_plain(latent_store_kernel, dim3(T_), dim3(THREADS), 0, stream, down, d_dtype, ldd, c_off,
-                      r_off, gain, eps, inv_freq, rot, positions, seq_of_token, page_table, pt_stride,
+                      r_off, gain, eps, inv_freq, rot, layout, mag, positions, seq_of_token, page_table, pt_stride,
                       c_pool, r_pool, pool_dtype, R, r, page_size, num_pages, err));
   DSP_CHECK_LAUNCH("dsp_latent_store");
   return 0;
 }
 
 extern "C" int dsp_attn_latent(const float* qa, long ldqa, const void* q, int q_dtype, long ldq,
-                               int q_head_stride, int qr_off, const float* inv_freq, int rot,
-                               const void* c_pool, const void* r_pool, int pool_dtype,
+                               int q_head_stride, int qr_off, const float* inv_freq, int rot, int layout,
+                               float mag, int window, const void* c_pool, const void* r_pool, int pool_dtype,
                                const int* page_table, int pt_stride, const int* positions,
                                const int* seq_of_token, void* out, int out_dtype, long ldo, int T_, int H,
                                int R, int r, int page_size, int num_pages, float scale,
@@ -261,7 +284,8 @@ extern "C" int dsp_attn_latent(const float* qa, long ldqa, const void* q, int q_
   DSP_REQUIRE(H > 0 && (H + GCHUNK - 1) / GCHUNK <= 65535, "dsp_attn_latent: H=%d", H);
   DSP_REQUIRE(R > 0 && R <= THREADS * 8, "dsp_attn_latent: latent size %d outside (0, %d]", R, THREADS * 8);
   DSP_REQUIRE(rot >= 0 && rot <= r && rot % 2 == 0 && (rot == 0 || inv_freq), "dsp_attn_latent: rot=%d of %d", rot, r);
-#define DSP_LATENT_ARGS qa, ldqa, q, q_dtype, ldq, q_head_stride, qr_off, inv_freq, rot, c_pool, r_pool, page_table, \
+  DSP_REQUIRE((layout == 0 || layout == 1) && window >= 0, "dsp_attn_latent: layout=%d window=%d", layout, window);
+#define DSP_LATENT_ARGS qa, ldqa, q, q_dtype, ldq, q_head_stride, qr_off, inv_freq, rot, layout, mag, window, c_pool, r_pool, page_table, \
                         pt_stride, positions, seq_of_token, out, out_dtype, ldo, T_, H, R, r, page_size, num_pages,  \
                         scale, err, stream
   const int dpt = (R + THREADS - 1) / THREADS;
@@ -303,7 +327,7 @@ constexpr int BM = 64, BN = 32, THREADS = 512, P_ROWB = 80, S_ROW = BN + 4;
 struct Args {
   const float* qa; long ldqa;
   const void* q; int q_dtype; long ldq; int q_head_stride, qr_off;
-  const float* inv_freq; int rot;
+  const float* inv_freq; int rot, layout; float mag; int window;
   const bf16* c_pool; const bf16* r_pool;
   const int* page_table; int pt_stride;
   const int* q_start; const int* ctx_len;
@@ -365,8 +389,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
   const int pos0 = clen - qlen + tok0;
   if (clen <= 0 || pos0 < 0 || ntok <= 0) return;  // a padding row of a captured step
   const int hi = pos0 + ntok - 1;
-  const int total = hi / BN + 1, per = (total + p.splits - 1) / p.splits;
-  const int kb = blockIdx.z * per, ke = min(total, kb + per);
+  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;  // the first key any row of the tile sees
+  const int first = lo / BN, total = hi / BN + 1, per = (total - first + p.splits - 1) / p.splits;
+  const int kb = first + blockIdx.z * per, ke = min(total, kb + per);
   const int* table = p.page_table + (size_t)seq * p.pt_stride;
   const int g = lane >> 2, c4 = lane & 3, m8 = lane >> 3, l8 = lane & 7;
   const int row_a = rg * 16 + g, row_b = row_a + 8;
@@ -388,7 +413,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
       const int row = warp + rr * (THREADS / 32);
       const int key = kt * BN + row;
       long at = -1;
-      if (key <= hi) {
+      if (key <= hi && key >= lo) {
         const int page = table[key / p.page_size];
         if (page < 0 || page >= p.num_pages) {
           if (lane == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
@@ -426,12 +451,26 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
           const int j = d - p.R;
           v0 = ld_any(p.q, p.q_dtype, at + j);
           v1 = ld_any(p.q, p.q_dtype, at + j + 1);
-          if (j < p.rot) {
+          if (j < p.rot && p.layout == 0) {
             float sn, cs;
             sincosf((float)(pos0 + tk) * p.inv_freq[j >> 1], &sn, &cs);
+            sn *= p.mag;
+            cs *= p.mag;
             const float u = v0, w = v1;
             v0 = u * cs - w * sn;
             v1 = w * cs + u * sn;
+          } else if (j < p.rot) {  // halves: each of the two elements with its partner in the other half
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const PairOf pr = pair_of(j + e, p.rot, 1);
+              float sn, cs;
+              sincosf((float)(pos0 + tk) * p.inv_freq[pr.freq], &sn, &cs);
+              sn *= p.mag;
+              cs *= p.mag;
+              const float mine = e ? v1 : v0, other = ld_any(p.q, p.q_dtype, at + pr.other);
+              const float turned = pr.second ? mine * cs + other * sn : mine * cs - other * sn;
+              if (e) v1 = turned; else v0 = turned;
+            }
           }
         }
       }
@@ -446,6 +485,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
     for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int pos_a = row_a < nrows ? pos0 + row_a / hc : -1, pos_b = row_b < nrows ? pos0 + row_b / hc : -1;
+  const int reach = p.window > 0 ? p.window : 0x40000000;
 
   for (int kt = kb; kt < ke; ++kt) {
     const int buf = (kt - kb) & 1;
@@ -493,10 +533,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
       s[3] += vb.y;
     }
     const int key0 = kt * BN + cg * 8 + 2 * c4;
-    s[0] = key0 <= pos_a ? s[0] * p.scale_log2 : -INFINITY;
-    s[1] = key0 + 1 <= pos_a ? s[1] * p.scale_log2 : -INFINITY;
-    s[2] = key0 <= pos_b ? s[2] * p.scale_log2 : -INFINITY;
-    s[3] = key0 + 1 <= pos_b ? s[3] * p.scale_log2 : -INFINITY;
+    // a row sees the keys (its position - reach, its position]
+    s[0] = (key0 <= pos_a && key0 > pos_a - reach) ? s[0] * p.scale_log2 : -INFINITY;
+    s[1] = (key0 + 1 <= pos_a && key0 + 1 > pos_a - reach) ? s[1] * p.scale_log2 : -INFINITY;
+    s[2] = (key0 <= pos_b && key0 > pos_b - reach) ? s[2] * p.scale_log2 : -INFINITY;
+    s[3] = (key0 + 1 <= pos_b && key0 + 1 > pos_b - reach) ? s[3] * p.scale_log2 : -INFINITY;
     float tmax[2] = {fmaxf(s[0], s[1]), fmaxf(s[2], s[3])};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -606,8 +647,8 @@ int launch(const Args& a, int num_tiles, int head_chunks, cudaStream_t stream) {
 // flat token * H + head.  Sizes: R a multiple of 64 up to 512 (not 320 or 448), r a multiple of 16,
 // row strides of qa in pairs of floats, pools and out in bfloat16.
 extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, int q_dtype, long ldq,
-                                   int q_head_stride, int qr_off, const float* inv_freq, int rot,
-                                   const void* c_pool, const void* r_pool, const int* page_table,
+                                   int q_head_stride, int qr_off, const float* inv_freq, int rot, int layout,
+                                   float mag, int window, const void* c_pool, const void* r_pool, const int* page_table,
                                    int pt_stride, const int* q_start, const int* ctx_len,
                                    const int* tile_seq, const int* tile_tok0, int tile_offset,
                                    int num_tiles, void* out, long ldo, float* part_o, float* part_ml,
@@ -617,6 +658,7 @@ extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, in
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_attn_latent_mma: no device error word");
   DSP_REQUIRE(R % 64 == 0 && r % 16 == 0 && r >= 0 && rot % 2 == 0 && rot <= r, "dsp_attn_latent_mma: R=%d r=%d rot=%d", R, r, rot);
+  DSP_REQUIRE((layout == 0 || layout == 1) && window >= 0, "dsp_attn_latent_mma: layout=%d window=%d", layout, window);
   DSP_REQUIRE(ldqa % 2 == 0 && ((uintptr_t)qa % 8) == 0 && ldo % 2 == 0 && ((uintptr_t)out % 4) == 0 &&
               ((uintptr_t)c_pool % 16) == 0 && ((uintptr_t)r_pool % 16) == 0, "dsp_attn_latent_mma: operand alignment");
   DSP_REQUIRE(splits >= 1 && (splits == 1 || (part_o && part_ml)), "dsp_attn_latent_mma: splits=%d without scratch", splits);
@@ -624,7 +666,7 @@ extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, in
   DSP_REQUIRE(TPT >= 1 && TPT * HC <= tc::BM, "dsp_attn_latent_mma: %d tokens x %d heads exceed a tile", TPT, HC);
   tc::Args a;
   a.qa = qa; a.ldqa = ldqa; a.q = q; a.q_dtype = q_dtype; a.ldq = ldq; a.q_head_stride = q_head_stride; a.qr_off = qr_off;
-  a.inv_freq = inv_freq; a.rot = rot; a.c_pool = (const bf16*)c_pool; a.r_pool = (const bf16*)r_pool;
+  a.inv_freq = inv_freq; a.rot = rot; a.layout = layout; a.mag = mag; a.window = window; a.c_pool = (const bf16*)c_pool; a.r_pool = (const bf16*)r_pool;
   a.page_table = page_table; a.pt_stride = pt_stride; a.q_start = q_start; a.ctx_len = ctx_len;
   a.tile_seq = tile_seq; a.tile_tok0 = tile_tok0; a.tile_offset = tile_offset;
   a.out = (bf16*)out; a.ldo = ldo; a.part_o = part_o; a.part_ml = part_ml; a.splits = splits;

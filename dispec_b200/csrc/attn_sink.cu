@@ -15,8 +15,14 @@
 //   * with `v_inv_freq` (float [Dv/2]): turns pairs (m, m + Dv/2) of every value head by
 //     position * v_inv_freq[m], after the norm (the attention kernel turns its result back by the
 //     query's position, so that a value enters the sum turned by the distance),
+//   * with `qt_every` > 0: multiplies every query by 1 + qt_coef * ln(floor((position + 1) / qt_every) + 1),
 //   * writes the query to `q_out` [T, H * Dk] and the key and the value to the pages (pools
 //     [num_pages, G, page_size, Dk] and [.., Dv]) in the pools' type.
+// With `maps` = M > 1 every query and key head consists of M parts of Dk values that are normed and
+// turned each on its own (the row holds H * M query parts, G * M key parts, G values): a key head is
+// cached as its parts side by side (width M * Dk), and query part m of head h goes out as a row of
+// M * Dk values that is zero outside part m, so that its product with the cached key head is the
+// product of the two parts m and the M maps of a head read the same key and value rows.
 // Everything between the loads and the stores is 32-bit.  A row with a negative position (padding
 // of a captured step) is skipped; a page id outside the pool is recorded in the device error word
 // and nothing is stored.
@@ -37,7 +43,8 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
                         long ld_vo, const float* __restrict__ lambda, const float* __restrict__ q_norm_w,
                         const float* __restrict__ k_norm_w, float norm_eps, int v_norm,
                         const float* __restrict__ v_inv_freq, void* __restrict__ q_out, long ld_q, int H,
-                        int G, int Dk, int Dv, int page_size, int num_pages, int write_kv, int* err) {
+                        int G, int Dk, int Dv, int maps, float qt_coef, int qt_every, int page_size, int num_pages,
+                        int write_kv, int* err) {
   extern __shared__ float cs[];  // [rot/2] cosines, [rot/2] sines; [Dv/2] + [Dv/2] for the values; [H + 2 G] head factors
   const int t = blockIdx.x;
   const int pos = positions[t];
@@ -49,8 +56,12 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &cs[half + i], &cs[i]);
   for (int i = threadIdx.x; i < vhalf; i += blockDim.x) sincosf((float)pos * v_inv_freq[i], &vcs[vhalf + i], &vcs[i]);
   const size_t row = (size_t)t * ld;
+  const int G_v = G;
+  H *= maps;  // from here on H and G count the parts of query and key heads
+  G *= maps;
   const size_t k0 = row + (size_t)H * Dk, v0 = k0 + (size_t)G * Dk;
-  for (int h = warp; h < H + 2 * G; h += warps) {
+  const float q_temp = qt_every > 0 ? 1.f + qt_coef * logf((float)((pos + 1) / qt_every) + 1.f) : 1.f;
+  for (int h = warp; h < H + G + G_v; h += warps) {
     const bool is_v = h >= H + G;
     const bool wanted = is_v ? v_norm != 0 : (h < H ? q_norm_w != nullptr : k_norm_w != nullptr);
     float r = 1.f;
@@ -75,9 +86,18 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
     const float o = ld_any(qkv, in_dtype, head0 + j) * f * (w ? w[j] : 1.f);
     return i < half ? v * cs[i] - o * cs[half + i] : v * cs[j] + o * cs[half + j];
   };
-  for (int idx = threadIdx.x; idx < H * Dk; idx += blockDim.x) {
-    const int h = idx / Dk;
-    st_any(q_out, pool_dtype, (size_t)t * ld_q + idx, turned(row + (size_t)h * Dk, idx % Dk, inv[h], q_norm_w));
+  if (maps == 1) {
+    for (int idx = threadIdx.x; idx < H * Dk; idx += blockDim.x) {
+      const int h = idx / Dk;
+      st_any(q_out, pool_dtype, (size_t)t * ld_q + idx, turned(row + (size_t)h * Dk, idx % Dk, inv[h], q_norm_w) * q_temp);
+    }
+  } else {
+    const int wide = maps * Dk;
+    for (int idx = threadIdx.x; idx < H * wide; idx += blockDim.x) {
+      const int h = idx / wide, part = (idx % wide) / Dk;
+      const float v = part == h % maps ? turned(row + (size_t)h * Dk, idx % Dk, inv[h], q_norm_w) * q_temp : 0.f;
+      st_any(q_out, pool_dtype, (size_t)t * ld_q + idx, v);
+    }
   }
   if (!write_kv) return;
   const int page = page_table[(size_t)seq_of_token[t] * pt_stride + pos / page_size];
@@ -86,8 +106,8 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
     return;
   }
   for (int idx = threadIdx.x; idx < G * Dk; idx += blockDim.x) {
-    const int g = idx / Dk, i = idx % Dk;
-    const size_t dst = (((size_t)page * G + g) * page_size + pos % page_size) * Dk + i;
+    const int g = idx / Dk, i = idx % Dk;  // part g of the key heads: part g % maps of head g / maps
+    const size_t dst = (((size_t)page * G_v + g / maps) * page_size + pos % page_size) * (maps * Dk) + (g % maps) * Dk + i;
     st_any(k_pool, pool_dtype, dst, turned(k0 + (size_t)g * Dk, i, inv[H + g], k_norm_w));
   }
   const float lam = (v_other && lambda) ? *lambda : 0.f;
@@ -96,7 +116,7 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
     if (v_other) v = (1.f - lam) * v + lam * ld_any(v_other, vo_dtype, (size_t)t * ld_vo + (size_t)g * Dv + i);
     return v * inv[H + G + g];
   };
-  for (int idx = threadIdx.x; idx < G * Dv; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < G_v * Dv; idx += blockDim.x) {
     const int g = idx / Dv, i = idx % Dv;
     float v = value(g, i);
     if (vhalf) {
@@ -104,7 +124,7 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
       const float o = value(g, j);
       v = i < vhalf ? v * vcs[i] - o * vcs[vhalf + i] : v * vcs[j] + o * vcs[vhalf + j];
     }
-    const size_t dst = (((size_t)page * G + g) * page_size + pos % page_size) * Dv + i;
+    const size_t dst = (((size_t)page * G_v + g) * page_size + pos % page_size) * Dv + i;
     st_any(v_pool, pool_dtype, dst, v);
   }
 }
@@ -168,10 +188,11 @@ extern "C" int dsp_qkv_rotate_store(const void* qkv, int in_dtype, long ld, cons
                                     const void* v_other, int vo_dtype, long ld_vo, const float* lambda,
                                     const float* q_norm_w, const float* k_norm_w, float norm_eps, int v_norm,
                                     const float* v_inv_freq, void* q_out,
-                                    long ld_q, int T, int H, int G, int Dk, int Dv, int page_size, int num_pages,
-                                    int write_kv, cudaStream_t stream) {
+                                    long ld_q, int T, int H, int G, int Dk, int Dv, int maps, float qt_coef,
+                                    int qt_every, int page_size, int num_pages, int write_kv, cudaStream_t stream) {
   if (T == 0) return 0;
   DSP_REQUIRE(qkv && positions && q_out && H > 0 && G > 0 && Dk > 0 && Dv > 0, "dsp_qkv_rotate_store: missing operand");
+  DSP_REQUIRE(maps >= 1 && qt_every >= 0, "dsp_qkv_rotate_store: maps=%d, qt_every=%d", maps, qt_every);
   DSP_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= Dk && (rot == 0 || inv_freq), "dsp_qkv_rotate_store: rot=%d for keys of %d", rot, Dk);
   DSP_REQUIRE(!write_kv || (k_pool && v_pool && page_table && seq_of_token && page_size > 0),
               "dsp_qkv_rotate_store: no pools to write to");
@@ -180,12 +201,12 @@ extern "C" int dsp_qkv_rotate_store(const void* qkv, int in_dtype, long ld, cons
   DSP_REQUIRE(!v_inv_freq || Dv % 2 == 0, "dsp_qkv_rotate_store: values of an odd width %d cannot be turned", Dv);
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_qkv_rotate_store: no device error word");
-  const size_t smem = (size_t)(rot + (v_inv_freq ? Dv : 0) + H + 2 * G) * sizeof(float);
+  const size_t smem = (size_t)(rot + (v_inv_freq ? Dv : 0) + (H + G) * maps + G) * sizeof(float);
   DSP_REQUIRE(smem <= 48 * 1024, "dsp_qkv_rotate_store: %d heads of %d and %d are more than the kernel holds", H, Dk, Dv);
   DSP_CUDA(launch_plain(qkv_rotate_store_kernel, dim3(T), dim3(256), smem, stream, qkv, in_dtype,
                         ld, positions, seq_of_token, page_table, pt_stride, k_pool, v_pool, pool_dtype, inv_freq, rot,
                         v_other, vo_dtype, ld_vo, lambda, q_norm_w, k_norm_w, norm_eps, v_norm, v_inv_freq, q_out, ld_q,
-                        H, G, Dk, Dv, page_size, num_pages, write_kv, err));
+                        H, G, Dk, Dv, maps, qt_coef, qt_every, page_size, num_pages, write_kv, err));
   DSP_CHECK_LAUNCH("dsp_qkv_rotate_store");
   return 0;
 }

@@ -7,6 +7,11 @@
 //                    is its largest score, only experts of the `keep` best groups can be chosen;
 //                    the `top` largest of those are the token's experts, their scores its weights
 //                    (not renormalised).  Equal scores: the lower index wins.  One block per token.
+//                    `group_kind` 1: a group's score is the sum of its two largest scores instead.
+//                    `normalize`: the weights are the chosen scores divided by their sum (+ 1e-20),
+//                    times `weight_scale`.  `extra` > 0: W_router has that many more rows after the
+//                    experts'; the sigmoids of their logits go to `extra_out` [T, extra] (gates that
+//                    are formed from the same row in the same 32-bit arithmetic).
 //   dsp_moe_plan     counts the (token, choice) pairs per expert, lists the pairs expert by expert
 //                    and cuts every expert's run into tiles of TILE_ROWS rows.  One block.
 //   dsp_moe_product  C[c_row(i)] = act(A[a_row(i)] B_e^T) for the sorted pairs i of every expert e
@@ -16,13 +21,14 @@
 //                    two matrices' rows in turn), both times row_scale[pair] when that is given (a
 //                    factor on the pair's input row, applied to the 32-bit sums, which is the same
 //                    product), g = min(gate, limit), u = clamp(up, -limit, limit),
-//                    C[., j] = g * sigmoid(alpha * g) * (u + 1); C is N / 2 wide.
+//                    C[., j] = g * sigmoid(alpha * g) * (u + up_shift); C is N / 2 wide (limit +inf,
+//                    alpha 1 and up_shift 0: silu(gate) * up).
 //                    Every output is one chain of fused
 //                    multiply-adds in ascending k, so a pair's result depends on nothing but its own
 //                    row and its expert.  With `tensor_cores` (bfloat16 operands): mma.sync tiles of
 //                    64 pairs (1) or 128 pairs (2); the plan must have been made for tiles of that many rows.
-//   dsp_moe_combine  y[t] = base[t] + sum_k weight[t, k] * P[t * top + k], in ascending k (without
-//                    `base`: from 0; without `weight`: every weight 1).
+//   dsp_moe_combine  y[t] = base[t] * base_scale[t] + sum_k weight[t, k] * P[t * top + k], in ascending k
+//                    (without `base`: from 0; without `base_scale`: 1; without `weight`: every weight 1).
 #include "common.cuh"
 
 namespace {
@@ -33,9 +39,9 @@ constexpr int MMA_ROWS = 64, MMA_ROWS_WIDE = 128, MMA_COLS = 128, MMA_K = 64, MM
 constexpr int MMA_LD = MMA_K + MMA_PAD;
 constexpr size_t mma_smem_bytes(int rows, int stages) { return sizeof(bf16) * stages * (rows + MMA_COLS) * MMA_LD; }
 
-__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha, float up_shift) {
   const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
-  return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
+  return g * (1.f / (1.f + expf(-alpha * g))) * (u + up_shift);
 }
 
 struct Best {
@@ -59,19 +65,20 @@ __device__ __forceinline__ Best warp_best(Best b) {
 
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float* __restrict__ w, int T, int W, int E,
-                 int groups, int keep, int top, int score_kind, int* __restrict__ ids, float* __restrict__ wts) {
+                 int groups, int keep, int top, int score_kind, int group_kind, int normalize, float weight_scale,
+                 int extra, float* __restrict__ extra_out, int* __restrict__ ids, float* __restrict__ wts) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const long t = blockIdx.x;
-  float* sc = sm;              // [E] scores
-  float* ok = sc + E;          // [E] 1: may still be chosen
+  float* sc = sm;              // [E + extra] scores (logits of the extra rows)
+  float* ok = sc + E + extra;  // [E] 1: may still be chosen
   float* gb = ok + E;          // [groups] best score of each group
   float* hs = gb + groups;     // [W] the token's row
   for (int i = threadIdx.x; i < W; i += blockDim.x) hs[i] = ld_any(h, h_dtype, (size_t)t * ldh + i);
   __syncthreads();
   // every expert's logit is the same sum whatever the block's shape: lane i takes columns i, i + 32, ...
   // in four interleaved chains (so that four loads are in flight), added in a fixed order
-  for (int e = warp; e < E; e += warps) {
+  for (int e = warp; e < E + extra; e += warps) {
     const float* we = w + (size_t)e * W;
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     int i = lane;
@@ -88,6 +95,7 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
   }
   __syncthreads();
   if (warp != 0) return;
+  for (int j = lane; j < extra; j += 32) extra_out[t * extra + j] = 1.f / (1.f + expf(-sc[E + j]));
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
   mx = warp_max(mx);
@@ -104,8 +112,21 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
   __syncwarp();
   const int per = E / groups;
   for (int g = lane; g < groups; g += 32) {
-    float b = -INFINITY;
-    for (int j = 0; j < per; ++j) b = fmaxf(b, sc[g * per + j]);
+    float b = -INFINITY, b2 = -INFINITY;  // the group's largest and second largest
+    for (int j = 0; j < per; ++j) {
+      const float v = sc[g * per + j];
+      if (v > b) {
+        b2 = b;
+        b = v;
+      } else {
+        b2 = fmaxf(b2, v);
+      }
+    }
+    if (group_kind == 1) {  // the sum of the two largest scores (of the sigmoids, where sc holds logits)
+      const float s1 = score_kind == 1 ? 1.f / (1.f + expf(-b)) : b;
+      const float s2 = per < 2 ? 0.f : score_kind == 1 ? 1.f / (1.f + expf(-b2)) : b2;
+      b = s1 + s2;
+    }
     gb[g] = b;
   }
   __syncwarp();
@@ -128,6 +149,12 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
       if (b.i >= 0) ok[b.i] = 0.f;
     }
     __syncwarp();
+  }
+  if (normalize && lane == 0) {
+    float sum = 0.f;
+    for (int r = 0; r < top; ++r) sum += wts[t * top + r];
+    const float f = weight_scale / (sum + 1e-20f);
+    for (int r = 0; r < top; ++r) wts[t * top + r] *= f;
   }
 }
 
@@ -175,7 +202,7 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
                    const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
                    const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                    const int* __restrict__ n_tiles, int N, int K, int act, const float* __restrict__ row_scale,
-                   float limit, float alpha) {
+                   float limit, float alpha, float up_shift) {
   const int tile = blockIdx.x;
   if (tile >= *n_tiles) return;
   __shared__ float As[TILE_K][TILE_ROWS + 1];
@@ -226,7 +253,7 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
       for (int j = 0; j < 4; j += 2) {
         const int n = n0 + tx * 4 + j;
         if (n + 1 >= N) continue;
-        st_any(C, c_dtype, (size_t)cr * ldc + n / 2, clamped_glu(acc[i][j] * f, acc[i][j + 1] * f, limit, alpha));
+        st_any(C, c_dtype, (size_t)cr * ldc + n / 2, clamped_glu(acc[i][j] * f, acc[i][j + 1] * f, limit, alpha, up_shift));
       }
       continue;
     }
@@ -271,7 +298,7 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
                        const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
                        const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                        const int* __restrict__ n_tiles, int N, int K, int act, const float* __restrict__ row_scale,
-                       float limit, float alpha) {
+                       float limit, float alpha, float up_shift) {
   const int tile = blockIdx.x;
   if (tile >= *n_tiles) return;
   extern __shared__ __align__(16) unsigned char mma_smem[];
@@ -357,7 +384,7 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
           const int n = n0 + wn * 64 + j * 8 + (lane & 3) * 2;
           if (n + 1 >= N) continue;
           st_any(C, c_dtype, (size_t)cr * ldc + n / 2,
-                 clamped_glu(acc[i][j][half * 2] * f, acc[i][j][half * 2 + 1] * f, limit, alpha));
+                 clamped_glu(acc[i][j][half * 2] * f, acc[i][j][half * 2 + 1] * f, limit, alpha, up_shift));
         }
         continue;
       }
@@ -379,13 +406,13 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restrict__ wts, const int* __restrict__ ids,
-                   const float* __restrict__ base, long ldb, float* __restrict__ y, long ldy, long T, int top,
-                   int width) {
+                   const float* __restrict__ base, long ldb, const float* __restrict__ base_scale,
+                   float* __restrict__ y, long ldy, long T, int top, int width) {
   const long n = T * width;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
     const long t = i / width;
     const int c = (int)(i % width);
-    float acc = base ? base[(size_t)t * ldb + c] : 0.f;
+    float acc = base ? base[(size_t)t * ldb + c] * (base_scale ? base_scale[t] : 1.f) : 0.f;
     for (int k = 0; k < top; ++k)
       if (ids[t * top + k] >= 0) acc = fmaf(wts ? wts[t * top + k] : 1.f, P[(size_t)(t * top + k) * ldp + c], acc);
     y[(size_t)t * ldy + c] = acc;
@@ -397,20 +424,23 @@ moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restric
 extern "C" int dsp_moe_tile_rows(int tensor_cores) { return tensor_cores == 2 ? MMA_ROWS_WIDE : tensor_cores ? MMA_ROWS : TILE_ROWS; }
 
 extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* w, int T, int W, int E, int groups,
-                             int keep, int top, int score_kind, int* ids, float* wts, cudaStream_t stream) {
+                             int keep, int top, int score_kind, int group_kind, int normalize, float weight_scale,
+                             int extra, float* extra_out, int* ids, float* wts, cudaStream_t stream) {
   if (T == 0) return 0;
   DSP_REQUIRE(score_kind == 0 || score_kind == 1, "dsp_moe_route: unknown score kind %d", score_kind);
   DSP_REQUIRE(h && w && ids && wts, "dsp_moe_route: missing operand");
+  DSP_REQUIRE((group_kind == 0 || group_kind == 1) && extra >= 0 && (extra == 0 || extra_out),
+              "dsp_moe_route: group kind %d, %d extra rows", group_kind, extra);
   DSP_REQUIRE(E > 0 && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && top > 0 &&
                   top <= keep * (E / groups),
               "dsp_moe_route: experts=%d groups=%d keep=%d top=%d do not fit together", E, groups, keep, top);
-  const size_t smem = (size_t)(2 * E + groups + W) * sizeof(float);
+  const size_t smem = (size_t)(2 * E + extra + groups + W) * sizeof(float);
   DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts over a width of %d are more than the router kernel holds", E, W);
   // a warp an expert where the block can hold them: the logits are chains of dependent rounds of loads,
   // and a step of a few tokens waits for the longest chain (the sums do not depend on the block's shape)
-  const unsigned threads = 32u * (unsigned)min(max(E, 4), 32);
+  const unsigned threads = 32u * (unsigned)min(max(E + extra, 4), 32);
   DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)T), dim3(threads), smem, stream, h, h_dtype, ldh, w, T, W, E,
-                        groups, keep, top, score_kind, ids, wts));
+                        groups, keep, top, score_kind, group_kind, normalize, weight_scale, extra, extra_out, ids, wts));
   DSP_CHECK_LAUNCH("dsp_moe_route");
   return 0;
 }
@@ -433,8 +463,8 @@ extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int rows_per_til
 extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int* a_rows, int a_div, const void* B,
                                void* C, int c_dtype, long ldc, const int* c_rows, const int* tile_expert,
                                const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles, int N,
-                               int K, int act, const float* row_scale, float limit, float alpha, int tensor_cores,
-                               cudaStream_t stream) {
+                               int K, int act, const float* row_scale, float limit, float alpha, float up_shift,
+                               int tensor_cores, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
   DSP_REQUIRE(A && B && C && tile_expert && tile_row0 && tile_rows && n_tiles && a_div > 0, "dsp_moe_product: missing operand");
   DSP_REQUIRE(act >= 0 && act <= 2, "dsp_moe_product: unknown activation %d", act);
@@ -457,11 +487,11 @@ extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int*
     if (tensor_cores == 2)
       DSP_CUDA(launch_plain(moe_product_mma_kernel<MMA_ROWS_WIDE, 3>, mgrid, dim3(MMA_ROWS_WIDE * 2), mma_smem_bytes(MMA_ROWS_WIDE, 3),
                             stream, (const bf16*)A, lda, a_rows, a_div, (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert,
-                            tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
+                            tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha, up_shift));
     else
       DSP_CUDA(launch_plain(moe_product_mma_kernel<MMA_ROWS, 4>, mgrid, dim3(MMA_ROWS * 2), mma_smem_bytes(MMA_ROWS, 4), stream,
                             (const bf16*)A, lda, a_rows, a_div, (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert,
-                            tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
+                            tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha, up_shift));
     DSP_CHECK_LAUNCH("dsp_moe_product (tensor cores)");
     return 0;
   }
@@ -469,24 +499,25 @@ extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int*
   DSP_REQUIRE(grid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
   if (ab_dtype == DSP_F32) {
     DSP_CUDA(launch_plain(moe_product_kernel<float>, grid, dim3(256), 0, stream, (const float*)A, lda, a_rows, a_div,
-                          (const float*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
+                          (const float*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha, up_shift));
   } else {
     DSP_CUDA(launch_plain(moe_product_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)A, lda, a_rows, a_div,
-                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha));
+                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act, row_scale, limit, alpha, up_shift));
   }
   DSP_CHECK_LAUNCH("dsp_moe_product");
   return 0;
 }
 
 extern "C" int dsp_moe_combine(const float* P, long ldp, const float* wts, const int* ids, const float* base, long ldb,
-                               float* y, long ldy, long T, int top, int width, cudaStream_t stream) {
+                               const float* base_scale, float* y, long ldy, long T, int top, int width,
+                               cudaStream_t stream) {
   if (T == 0) return 0;
   DSP_REQUIRE(P && ids && y, "dsp_moe_combine: missing operand");
   const long n = T * width;
   const int sms = dsp_num_sms();
   const long want = (n + 255) / 256, cap = (long)(sms > 0 ? sms : 148) * 16;
   DSP_CUDA(launch_plain(moe_combine_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, P, ldp,
-                        wts, ids, base, ldb, y, ldy, T, top, width));
+                        wts, ids, base, ldb, base_scale, y, ldy, T, top, width));
   DSP_CHECK_LAUNCH("dsp_moe_combine");
   return 0;
 }

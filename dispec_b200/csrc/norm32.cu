@@ -252,6 +252,54 @@ __global__ void __launch_bounds__(256) softcap_kernel(float* x, long ldx, long r
   }
 }
 
+// x <- x * s (float rows): a constant factor on the logits.
+__global__ void __launch_bounds__(256) scale_rows_kernel(float* x, long ldx, long rows, int cols, float s) {
+  const long n = rows * cols;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    x[(size_t)(i / cols) * ldx + (i % cols)] *= s;
+}
+
+// y[t, j] = x[t, j] * sigmoid(gate[t, j / per]): an output gate with one number for every `per`
+// neighbouring columns (per 1: a gate per element; per = a head's width: a gate per head).
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(const void* __restrict__ x, int x_dtype, long ldx, const void* __restrict__ gate, int g_dtype,
+                    long ldg, int per, void* __restrict__ y, int y_dtype, long ldy, long rows, int cols) {
+  const long n = rows * cols;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / cols;
+    const int c = (int)(i % cols);
+    const float g = ld_any(gate, g_dtype, (size_t)r * ldg + c / per);
+    st_any(y, y_dtype, (size_t)r * ldy + c, ld_any(x, x_dtype, (size_t)r * ldx + c) / (1.f + expf(-g)));
+  }
+}
+
+// Differential heads.  a holds, per token, the results of `2 H` attention maps of width dv, the two
+// maps of head h next to each other (h * 2, h * 2 + 1).  Per (token, head):
+//   o = a1 - lambda * a2;  y = o / sqrt(mean(o^2) + eps) * post * sigmoid(gate[t, h])   (gate optional)
+// One warp per (token, head).
+__global__ void __launch_bounds__(128)
+diff_heads_kernel(const void* __restrict__ a, int a_dtype, long lda, float lambda, float post, float eps,
+                  const void* __restrict__ gate, int g_dtype, long ldg, void* __restrict__ y, int y_dtype, long ldy,
+                  int T, int H, int dv) {
+  const int lane = threadIdx.x & 31;
+  const long pair = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= (long)T * H) return;
+  const int t = (int)(pair / H), h = (int)(pair % H);
+  const size_t a1 = (size_t)t * lda + (size_t)(2 * h) * dv, a2 = a1 + dv;
+  float ss = 0.f;
+  for (int j = lane; j < dv; j += 32) {
+    const float o = fmaf(-lambda, ld_any(a, a_dtype, a2 + j), ld_any(a, a_dtype, a1 + j));
+    ss = fmaf(o, o, ss);
+  }
+  ss = warp_sum(ss);
+  float f = post / sqrtf(ss / (float)dv + eps);
+  if (gate) f /= 1.f + expf(-ld_any(gate, g_dtype, (size_t)t * ldg + h));
+  for (int j = lane; j < dv; j += 32) {
+    const float o = fmaf(-lambda, ld_any(a, a_dtype, a2 + j), ld_any(a, a_dtype, a1 + j));
+    st_any(y, y_dtype, (size_t)t * ldy + (size_t)h * dv + j, o * f);
+  }
+}
+
 // out32[t] = table[ids[t]] * scale: the embedding as the first value of a 32-bit stream.
 __global__ void __launch_bounds__(256)
 embed_scaled_kernel(const void* __restrict__ table, int t_dtype, int table_rows, const int* __restrict__ ids,
@@ -396,6 +444,36 @@ extern "C" int dsp_softcap(float* x, long ldx, long rows, int cols, float cap, c
   DSP_REQUIRE(x && cap > 0.f, "dsp_softcap: missing operand or cap <= 0");
   DSP_CUDA(launch_plain(softcap_kernel, dim3(flat_grid(rows * cols)), dim3(256), 0, stream, x, ldx, rows, cols, cap));
   DSP_CHECK_LAUNCH("dsp_softcap");
+  return 0;
+}
+
+extern "C" int dsp_scale_rows(float* x, long ldx, long rows, int cols, float s, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  DSP_REQUIRE(x, "dsp_scale_rows: missing operand");
+  DSP_CUDA(launch_plain(scale_rows_kernel, dim3(flat_grid(rows * cols)), dim3(256), 0, stream, x, ldx, rows, cols, s));
+  DSP_CHECK_LAUNCH("dsp_scale_rows");
+  return 0;
+}
+
+extern "C" int dsp_sigmoid_gate(const void* x, int x_dtype, long ldx, const void* gate, int g_dtype, long ldg, int per,
+                                void* y, int y_dtype, long ldy, long rows, int cols, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  DSP_REQUIRE(x && gate && y && per > 0, "dsp_sigmoid_gate: missing operand");
+  DSP_CUDA(launch_plain(sigmoid_gate_kernel, dim3(flat_grid(rows * cols)), dim3(256), 0, stream, x, x_dtype, ldx, gate,
+                        g_dtype, ldg, per, y, y_dtype, ldy, rows, cols));
+  DSP_CHECK_LAUNCH("dsp_sigmoid_gate");
+  return 0;
+}
+
+extern "C" int dsp_diff_heads(const void* a, int a_dtype, long lda, float lambda, float post, float eps, const void* gate,
+                              int g_dtype, long ldg, void* y, int y_dtype, long ldy, int T, int H, int dv,
+                              cudaStream_t stream) {
+  if (T == 0) return 0;
+  DSP_REQUIRE(a && y && H > 0 && dv > 0, "dsp_diff_heads: missing operand");
+  const long pairs = (long)T * H;
+  DSP_CUDA(launch_plain(diff_heads_kernel, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, a, a_dtype, lda, lambda,
+                        post, eps, gate, g_dtype, ldg, y, y_dtype, ldy, T, H, dv));
+  DSP_CHECK_LAUNCH("dsp_diff_heads");
   return 0;
 }
 

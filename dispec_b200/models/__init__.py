@@ -1,5 +1,5 @@
 """Built-in architectures; importing this package registers them."""
-from dispec_b200.models import desalix, murutar, puludra, qwen2  # noqa: F401
+from dispec_b200.models import desalix, milivik, murutar, puludra, qwen2  # noqa: F401
 from dispec_b200.models.model import DecoderModel
 from dispec_b200.models.spec import LayerCall, ModelSpec
 

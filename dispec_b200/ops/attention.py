@@ -313,7 +313,8 @@ def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: t
                      key_dim: int, value_dim: int, out_dtype: torch.dtype, v_other: torch.Tensor | None = None,
                      blend: torch.Tensor | None = None, q_norm: torch.Tensor | None = None,
                      k_norm: torch.Tensor | None = None, norm_eps: float = 0.0, v_norm: bool = False,
-                     v_inv_freq: torch.Tensor | None = None) -> torch.Tensor:
+                     v_inv_freq: torch.Tensor | None = None, maps: int = 1,
+                     q_temp: tuple | None = None) -> torch.Tensor:
     """From rows [q (H x Dk) | k (G x Dk) | v (G x Dv)] of a fused projection: turns pairs
     (i, i + rotary_dim/2) of every query and key head by position * inv_freq[i] in 32-bit, blends
     v <- (1 - blend) v + blend * v_other when ``v_other`` [T, G * Dv] is given (``blend``: a float32
@@ -325,15 +326,22 @@ def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: t
     divided by its root mean square (``norm_eps`` inside the root) and multiplied by the weight
     before it is turned.  ``v_norm``: every value head is divided by its root mean square (no
     weight).  ``v_inv_freq`` (float32 [Dv/2]): the value of position p is stored turned, pair
-    (m, m + Dv/2) by p * v_inv_freq[m], after the norm."""
+    (m, m + Dv/2) by p * v_inv_freq[m], after the norm.
+
+    ``q_temp`` = (coef, every): every query is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+    ``maps`` = M > 1: every query and key head has M parts of ``key_dim`` values, normed and turned
+    each on its own (the row holds H * M query parts, G * M key parts and G values).  A key head is
+    cached as its parts side by side (the "key" pool is M * Dk wide), and the queries come back as
+    [T, H * M rows of M * Dk]: part m of head h, zero outside columns m * Dk .. (m + 1) * Dk, so that
+    an attention with H * M query heads over the G cached key heads gives every part's map."""
     if not qkv.is_cuda:
         raise L.KernelError("qkv_rotate_store: CUDA tensors only (there is no CPU path)")
     T = qkv.shape[0]
     H, G, dk, dv = num_heads, num_kv_heads, key_dim, value_dim
-    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (H + G) * dk + G * dv
+    assert maps >= 1 and qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (H + G) * maps * dk + G * dv
     k_pool, v_pool = cache.key_pool, cache.value_pool
     num_pages, g_, page_size, dk_ = k_pool.shape
-    assert (g_, dk_) == (G, dk) and v_pool.shape == (num_pages, G, page_size, dv)
+    assert (g_, dk_) == (G, maps * dk) and v_pool.shape == (num_pages, G, page_size, dv)
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.dtype == v_pool.dtype == out_dtype
     table = cache.page_table
     assert table.dtype == torch.int32 and table.stride(1) == 1
@@ -347,14 +355,16 @@ def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: t
     if v_inv_freq is not None:
         assert dv % 2 == 0 and v_inv_freq.dtype == torch.float32 and v_inv_freq.is_contiguous()
         assert v_inv_freq.shape[0] >= dv // 2
-    q_out = torch.empty((T, H * dk), dtype=out_dtype, device=qkv.device)
+    q_out = torch.empty((T, H * maps * maps * dk), dtype=out_dtype, device=qkv.device)
+    qt_coef, qt_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     lib = L.mixer_library("attn_sink")
     L.check(lib.dsp_qkv_rotate_store(
         L.ptr(qkv), L.dtype_code(qkv.dtype), L.i64(qkv.stride(0)), L.ptr(positions), L.ptr(seq_of_token),
         L.ptr(table), table.stride(0), L.ptr(k_pool), L.ptr(v_pool), L.dtype_code(out_dtype), L.ptr(inv_freq),
         rotary_dim, L.ptr(v_other), L.dtype_code(v_other.dtype) if v_other is not None else 0,
         L.i64(v_other.stride(0) if v_other is not None else 0), L.ptr(blend if v_other is not None else None),
-        L.ptr(q_norm), L.ptr(k_norm), L.f32(norm_eps), int(bool(v_norm)), L.ptr(v_inv_freq), L.ptr(q_out), L.i64(q_out.stride(0)), T, H, G, dk, dv, page_size, num_pages, int(cache.write),
+        L.ptr(q_norm), L.ptr(k_norm), L.f32(norm_eps), int(bool(v_norm)), L.ptr(v_inv_freq), L.ptr(q_out), L.i64(q_out.stride(0)), T, H, G, dk, dv, maps, L.f32(qt_coef), qt_every, page_size,
+        num_pages, int(cache.write),
         L.stream_handle()))
     return q_out
 

@@ -9,13 +9,17 @@ import torch
 
 from dispec_b200.ops import library as L
 
+_LAYOUTS = {"interleaved": 0, "halves": 1}  # which dimensions form pair i: (2i, 2i+1) or (i, i + rot/2)
+
 
 def latent_store(down: torch.Tensor, c_off: int, r_off: int, gain: torch.Tensor, eps: float,
                  inv_freq: torch.Tensor | None, rot: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
-                 page_table: torch.Tensor, c_pool: torch.Tensor, r_pool: torch.Tensor) -> None:
+                 page_table: torch.Tensor, c_pool: torch.Tensor, r_pool: torch.Tensor,
+                 layout: str = "interleaved", magnitude: float = 1.0) -> None:
     """``down`` [T, columns]: rows of the down projection; columns c_off.. hold the R latent values
-    (RMS-normed here with ``gain``), columns r_off.. the r values of the shared key part (pairs
-    (2i, 2i+1) of its first ``rot`` values turned by position * inv_freq[i]).  Pools:
+    (RMS-normed here with ``gain``), columns r_off.. the r values of the shared key part (pair i
+    of its first ``rot`` values, (2i, 2i+1) or with ``layout`` "halves" (i, i + rot/2), turned by
+    position * inv_freq[i], cosine and sine times ``magnitude``).  Pools:
     [num_pages, 1, page_size, R] and [num_pages, 1, page_size, r]."""
     if not (down.is_cuda and c_pool.is_cuda):
         raise L.KernelError("latent_store: CUDA tensors only (there is no CPU path)")
@@ -32,7 +36,8 @@ def latent_store(down: torch.Tensor, c_off: int, r_off: int, gain: torch.Tensor,
     lib = L.mixer_library("attn_latent")
     L.check(lib.dsp_latent_store(
         L.ptr(down), L.dtype_code(down.dtype), L.i64(down.stride(0)), c_off, r_off, L.ptr(gain), L.f32(eps),
-        L.ptr(inv_freq), rot, L.ptr(positions), L.ptr(seq_of_token), L.ptr(page_table), page_table.stride(0),
+        L.ptr(inv_freq), rot, _LAYOUTS[layout], L.f32(magnitude), L.ptr(positions), L.ptr(seq_of_token),
+        L.ptr(page_table), page_table.stride(0),
         L.ptr(c_pool), L.ptr(r_pool), L.dtype_code(c_pool.dtype), down.shape[0], R, r, page_size, num_pages,
         L.stream_handle()))
 
@@ -40,11 +45,13 @@ def latent_store(down: torch.Tensor, c_off: int, r_off: int, gain: torch.Tensor,
 def latent_attention(q_absorbed: torch.Tensor, q: torch.Tensor, q_head_stride: int, qr_off: int,
                      inv_freq: torch.Tensor | None, rot: int, c_pool: torch.Tensor, r_pool: torch.Tensor,
                      page_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
-                     num_heads: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+                     num_heads: int, scale: float, out_dtype: torch.dtype, layout: str = "interleaved",
+                     magnitude: float = 1.0, window: int = 0) -> torch.Tensor:
     """``q_absorbed`` float32 [T, H * R]: every head's query with the key map folded in.  ``q``
     [T, columns]: the projected queries; head h's part to be rotated starts at column
     h * q_head_stride + qr_off and has r values.  Returns sum_j softmax_j c_j per head as
-    [T, H * R] of ``out_dtype``; the query at position p sees every cached j <= p."""
+    [T, H * R] of ``out_dtype``; the query at position p sees every cached j <= p, with ``window``
+    W > 0 those with p - W < j.  ``layout`` / ``magnitude``: as in ``latent_store``."""
     if not (q_absorbed.is_cuda and c_pool.is_cuda):
         raise L.KernelError("latent_attention: CUDA tensors only (there is no CPU path)")
     num_pages, _, page_size, R = c_pool.shape
@@ -59,7 +66,8 @@ def latent_attention(q_absorbed: torch.Tensor, q: torch.Tensor, q_head_stride: i
     lib = L.mixer_library("attn_latent")
     L.check(lib.dsp_attn_latent(
         L.ptr(q_absorbed), L.i64(q_absorbed.stride(0)), L.ptr(q), L.dtype_code(q.dtype), L.i64(q.stride(0)),
-        q_head_stride, qr_off, L.ptr(inv_freq), rot, L.ptr(c_pool), L.ptr(r_pool), L.dtype_code(c_pool.dtype),
+        q_head_stride, qr_off, L.ptr(inv_freq), rot, _LAYOUTS[layout], L.f32(magnitude), int(window), L.ptr(c_pool),
+        L.ptr(r_pool), L.dtype_code(c_pool.dtype),
         L.ptr(page_table), page_table.stride(0), L.ptr(positions), L.ptr(seq_of_token), L.ptr(out),
         L.dtype_code(out_dtype), L.i64(out.stride(0)), T, num_heads, R, r, page_size, num_pages, L.f32(scale),
         L.stream_handle()))
@@ -96,7 +104,8 @@ def choose_key_splits(num_tiles: int, head_chunks: int, max_ctx: int, device) ->
 
 def latent_attention_tiles(ctx, q_absorbed: torch.Tensor, q: torch.Tensor, q_head_stride: int, qr_off: int,
                            inv_freq: torch.Tensor | None, rot: int, c_pool: torch.Tensor, r_pool: torch.Tensor,
-                           page_table: torch.Tensor, num_heads: int, scale: float) -> torch.Tensor:
+                           page_table: torch.Tensor, num_heads: int, scale: float, layout: str = "interleaved",
+                           magnitude: float = 1.0, window: int = 0) -> torch.Tensor:
     """The same attention on tensor cores (bfloat16 pools), over the step's tile list for
     ``mma_tokens_per_tile(num_heads)`` tokens a tile.  Single tokens (the first tiles) have their
     keys cut into ranges that are merged by ``dsp_attn_combine``; portions of prompts run whole."""
@@ -115,14 +124,16 @@ def latent_attention_tiles(ctx, q_absorbed: torch.Tensor, q: torch.Tensor, q_hea
     def launch(offset, count, splits, part_o, part_ml):
         L.check(lib.dsp_attn_latent_mma(
             L.ptr(q_absorbed), L.i64(q_absorbed.stride(0)), L.ptr(q), L.dtype_code(q.dtype), L.i64(q.stride(0)),
-            q_head_stride, qr_off, L.ptr(inv_freq), rot, L.ptr(c_pool), L.ptr(r_pool), L.ptr(page_table),
+            q_head_stride, qr_off, L.ptr(inv_freq), rot, _LAYOUTS[layout], L.f32(magnitude), int(window),
+            L.ptr(c_pool), L.ptr(r_pool), L.ptr(page_table),
             page_table.stride(0), L.ptr(ctx.q_start), L.ptr(ctx.ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), offset,
             count, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml), splits, num_heads, tpt, R, r,
             page_size, num_pages, L.f32(scale), L.stream_handle()))
 
     n_dec = ctx.num_decode_seqs  # single tokens come first, one tile each
     if n_dec:
-        splits = choose_key_splits(n_dec, chunks, ctx.max_ctx_len, q.device)
+        keys = min(ctx.max_ctx_len, window + MMA_KEYS_PER_TILE) if window > 0 else ctx.max_ctx_len
+        splits = choose_key_splits(n_dec, chunks, keys, q.device)
         if splits > 1:
             part_o, part_ml = attn_ops._partial_buffers(q.device, n_dec * num_heads, splits, R)
             launch(0, n_dec, splits, part_o, part_ml)

@@ -176,3 +176,45 @@ def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.
                                       L.f32(scale), L.ptr(out), L.i64(out.stride(0)), L.i64(ids.shape[0]),
                                       table.shape[1], L.stream_handle()))
     return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x <- x * factor in place (float32 rows)."""
+    _rows2d(x, "scale_")
+    assert x.dtype == torch.float32
+    L.check(L.core().dsp_scale_rows(L.ptr(x), L.i64(x.stride(0)), L.i64(x.shape[0]), x.shape[1], L.f32(factor),
+                                    L.stream_handle()))
+    return x
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y[t, j] = x[t, j] * sigmoid(gate[t, j // per]) with per = x's columns / gate's columns: a gate
+    per element (equal widths) or one number for each run of neighbouring columns (a head)."""
+    _rows2d(x, "sigmoid_gate")
+    _rows2d(gate, "sigmoid_gate")
+    assert gate.shape[0] == x.shape[0] and gate.shape[1] > 0 and x.shape[1] % gate.shape[1] == 0
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    L.check(L.core().dsp_sigmoid_gate(L.ptr(x), L.dtype_code(x.dtype), L.i64(x.stride(0)), L.ptr(gate),
+                                      L.dtype_code(gate.dtype), L.i64(gate.stride(0)), x.shape[1] // gate.shape[1],
+                                      L.ptr(y), L.dtype_code(out_dtype), L.i64(y.stride(0)), L.i64(x.shape[0]),
+                                      x.shape[1], L.stream_handle()))
+    return y
+
+
+def diff_heads(a: torch.Tensor, num_heads: int, lam: float, post: float, eps: float, out_dtype: torch.dtype,
+               gate: torch.Tensor | None = None) -> torch.Tensor:
+    """a [T, 2 H dv]: per token the results of two attention maps per head, side by side.  Returns
+    [T, H dv]: o = a1 - lam * a2, every head divided by its root mean square (eps inside the root),
+    times ``post`` and sigmoid(gate[t, h]) (``gate`` [T, H], optional).  32-bit arithmetic."""
+    _rows2d(a, "diff_heads")
+    assert a.shape[1] % (2 * num_heads) == 0
+    T, dv = a.shape[0], a.shape[1] // (2 * num_heads)
+    if gate is not None:
+        _rows2d(gate, "diff_heads")
+        assert gate.shape == (T, num_heads)
+    y = torch.empty((T, num_heads * dv), dtype=out_dtype, device=a.device)
+    L.check(L.core().dsp_diff_heads(L.ptr(a), L.dtype_code(a.dtype), L.i64(a.stride(0)), L.f32(lam), L.f32(post),
+                                    L.f32(eps), L.ptr(gate), L.dtype_code(gate.dtype) if gate is not None else 0,
+                                    L.i64(gate.stride(0) if gate is not None else 0), L.ptr(y), L.dtype_code(out_dtype),
+                                    L.i64(y.stride(0)), T, num_heads, dv, L.stream_handle()))
+    return y

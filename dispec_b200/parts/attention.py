@@ -12,10 +12,13 @@ projection without bias (:158,185).
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from dispec_b200 import ops
 from dispec_b200.ops import attention as attn_ops
+from dispec_b200.ops import norm32 as norm32_ops
 from dispec_b200.cache.manager import CacheTensor
 from dispec_b200.parts.base import CacheNeed, Mixer, TensorSpec
 from dispec_b200.registry import register_part
@@ -88,6 +91,8 @@ class GQAAttention(Mixer):
         rot = self.position_encoding.rotation()
         if rot is not None and rot.layout != "halves":
             raise ValueError(f"gqa_attention turns pairs (i, i + rotary_dim/2) only, not the {rot.layout!r} layout")
+        if rot is not None and rot.magnitude != 1.0:
+            raise ValueError("gqa_attention applies pure rotations only (the encoding has a magnitude)")
         inv_freq, rotary_dim = (rot.inv_freq, rot.rotary_dim) if rot is not None else (None, 0)
         scale = self.scale * self.position_encoding.score_scale()
         # single tokens come first in the batch: when their attention kernel rotates q and k itself and
@@ -205,6 +210,8 @@ class SinkAttention(Mixer):
         rot = self.position_encoding.rotation()
         if rot is not None and rot.layout != "halves":
             raise ValueError(f"sink_attention turns pairs (i, i + rotary_dim/2) only, not the {rot.layout!r} layout")
+        if rot is not None and rot.magnitude != 1.0:
+            raise ValueError("sink_attention applies pure rotations only (the encoding has a magnitude)")
         inv_freq, rotary_dim = (rot.inv_freq, rot.rotary_dim) if rot is not None else (None, 0)
         v_other = None
         if self.value_mix is not None:
@@ -225,3 +232,91 @@ class SinkAttention(Mixer):
                                       chunked=self.mask == "chunk", sink_values=self.sink_values,
                                       turn_freq=self.value_freq)
         return ops.linear(out, self.w_o, out_dtype=torch.float32)
+
+
+@register_part("mixer", "differential_attention")
+class DifferentialAttention(Mixer):
+    """Grouped-query attention with two softmax maps per head over the same values:
+
+        q = W_q h: per head two parts (map 1, map 2) of ``key_dim`` values; k = W_k h likewise per
+        key/value head; v = W_v h.  No biases.  With ``head_norm`` every part of q and k is divided
+        by its root mean square (``norm_eps`` inside the root) and multiplied by ``q.norm.weight`` /
+        ``k.norm.weight`` ([key_dim], one for all heads and maps); then turned by the position
+        encoding, if it turns anything.  ``q_temp`` = (coef, every): q at position p is multiplied by
+        1 + coef * ln(floor((p + 1) / every) + 1).
+        a_m = softmax over the visible keys of (q_m . k_m) * scale, times v        (m = 1, 2)
+        o = a_1 - lambda a_2,  lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff  (one number for the layer)
+        o <- o / sqrt(mean(o^2) + norm_eps) * (1 - diff) per head; with ``head_gate`` times
+        sigmoid(W_g h)_head, one number per head; output W_o on the concatenated heads.
+
+    The two parts of a key head are cached side by side as one key of width 2 * key_dim, and the
+    queries of the two maps are rows that are zero outside their own part (``qkv_rotate_store`` with
+    two maps): one attention with 2 H query heads over G key/value heads gives both maps, and each
+    key and value row is read once for both.  Keys visible to position p: j <= p, with ``window`` W > 0
+    those with p - W < j.  Scores, softmax, norms, the temperature and the combination are 32-bit."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                 scale: float, diff: float, norm_eps: float, position_encoding, window: int = 0,
+                 head_norm: bool = True, q_temp: tuple | None = None, head_gate: bool = True):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        if not float(scale) > 0.0:
+            raise ValueError(f"the attention scale must be positive, got {scale}")
+        if q_temp is not None and (len(q_temp) != 2 or int(q_temp[1]) < 1):
+            raise ValueError(f"q_temp must be None or (coef, every >= 1), got {q_temp!r}")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.key_dim, self.value_dim = key_dim, value_dim
+        self.scale, self.diff, self.norm_eps, self.window = float(scale), float(diff), float(norm_eps), int(window)
+        self.head_norm, self.head_gate = bool(head_norm), bool(head_gate)
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else None
+        self.position_encoding = position_encoding
+        self.w_in = self.w_o = self.q_norm = self.k_norm = None
+        self.lam = 0.0
+
+    def tensor_specs(self):
+        h, H, G, dk, dv = self.hidden_size, self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
+        specs = {"q.weight": TensorSpec((H * 2 * dk, h)), "k.weight": TensorSpec((G * 2 * dk, h)),
+                 "v.weight": TensorSpec((G * dv, h)), "o.weight": TensorSpec((h, H * dv))}
+        for n in ("lq1", "lk1", "lq2", "lk2"):
+            specs[n] = TensorSpec((dk,), dtype="float32")
+        if self.head_norm:
+            specs["q.norm.weight"] = TensorSpec((dk,), dtype="float32", init="one_plus_normal")
+            specs["k.norm.weight"] = TensorSpec((dk,), dtype="float32", init="one_plus_normal")
+        if self.head_gate:
+            specs["g.weight"] = TensorSpec((H, h))
+        return specs
+
+    def load(self, tensors):
+        rows = [tensors["q.weight"], tensors["k.weight"], tensors["v.weight"]]
+        if self.head_gate:  # the gates' rows ride in the input product
+            rows.append(tensors["g.weight"])
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors["o.weight"]
+        self.q_norm, self.k_norm = tensors.get("q.norm.weight"), tensors.get("k.norm.weight")
+        dot = lambda a, b: float((tensors[a].double() * tensors[b].double()).sum())
+        self.lam = math.exp(dot("lq1", "lk1")) - math.exp(dot("lq2", "lk2")) + self.diff
+
+    def cache_need(self):
+        return CacheNeed((CacheTensor("key", self.num_kv_heads, 2 * self.key_dim),
+                          CacheTensor("value", self.num_kv_heads, self.value_dim)), self.window)
+
+    def tokens_per_attention_tile(self):
+        return attn_ops.sink_tokens_per_tile(2 * self.num_heads // self.num_kv_heads, 2 * self.key_dim, self.value_dim)
+
+    def forward(self, ctx, x, cache, state):
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
+        z = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [q parts | k parts | v | gates]
+        n_qkv = (H + G) * 2 * dk + G * dv
+        rot = self.position_encoding.rotation()
+        if rot is not None and (rot.layout != "halves" or rot.magnitude != 1.0):
+            raise ValueError("differential_attention turns pairs (i, i + rotary_dim/2) by pure rotations only")
+        inv_freq, rotary_dim = (rot.inv_freq, rot.rotary_dim) if rot is not None else (None, 0)
+        q = attn_ops.qkv_rotate_store(z[:, :n_qkv], ctx.positions, ctx.seq_of_token, cache, inv_freq, rotary_dim, H, G,
+                                      dk, dv, ctx.dtype, q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.norm_eps,
+                                      maps=2, q_temp=self.q_temp)
+        maps = torch.empty((q.shape[0], 2 * H * dv), dtype=q.dtype, device=q.device)
+        attn_ops.sink_paged_attention(ctx, q, cache, maps, 2 * H, G, 2 * dk, dv, self.window,
+                                      self.scale * self.position_encoding.score_scale(), False)
+        heads = norm32_ops.diff_heads(maps, H, self.lam, 1.0 - self.diff, self.norm_eps, ctx.dtype,
+                                      gate=z[:, n_qkv:] if self.head_gate else None)
+        return ops.linear(heads, self.w_o, out_dtype=torch.float32)

@@ -120,10 +120,13 @@ class Norm(Part):
 class Rotation:
     """Rotation of query and key heads: pair i of every head is turned by the angle
     position * inv_freq[i]; dimensions from ``rotary_dim`` on pass unchanged.  ``layout`` says
-    which dimensions form pair i: "halves" (i, i + rotary_dim/2) or "interleaved" (2i, 2i+1)."""
+    which dimensions form pair i: "halves" (i, i + rotary_dim/2) or "interleaved" (2i, 2i+1).
+    ``magnitude``: a factor on cosine and sine (1: a pure rotation); a mixer whose kernels do not
+    apply it refuses an encoding that has one."""
     inv_freq: Any  # float32 [rotary_dim / 2] on the device
     rotary_dim: int
     layout: str = "halves"
+    magnitude: float = 1.0
 
 
 class PositionEncoding(Part):

@@ -230,6 +230,52 @@ class SandwichNormBlock(Block):
         return x, nxt
 
 
+@register_part("block", "output_norm")
+class OutputNormBlock(Block):
+    """A norm on every sublayer's result only, on a residual stream kept in 32-bit floats
+    (``WideStream``):
+
+        x <- x + out_norm1(mixer(x))
+        x <- x + out_norm2(ffn(x))            (if there is a feed-forward)
+
+    The sublayers read the stream itself (rounded to the model type for their products; on the
+    32-bit path the stream's own rows).  The norms are RMS norms given as parts with a float32
+    ``weight`` per coordinate and an ``eps`` (``rms_norm_f32``); the sublayers return 32-bit rows.
+    Each sum runs as one kernel: RMS of the addend, gain, sum, and the rounded copy of the new
+    stream that the next sublayer reads.  The block hands that copy of its result on as ``pending``
+    when the block that follows asks for it (``first_norm_after_product`` answers with no norm)."""
+
+    def __init__(self, hidden_size: int, mixer, mixer_out_norm, feed_forward=None, ffn_out_norm=None):
+        if (feed_forward is None) != (ffn_out_norm is None):
+            raise ValueError("output_norm: a feed-forward and its norm come together or not at all")
+        self.hidden_size = hidden_size
+        self.mixer, self.mixer_out_norm = mixer, mixer_out_norm
+        self.feed_forward, self.ffn_out_norm = feed_forward, ffn_out_norm
+
+    def first_norm_after_product(self):
+        return None, 0.0  # no norm in front of the mixer: the rows themselves, in the products' type
+
+    def forward(self, ctx, x, pending, cache, state, then_norm=None):
+        if not isinstance(x, WideStream) or x.full.dtype != torch.float32:
+            raise ValueError("output_norm: the residual stream must be a 32-bit WideStream")
+        full = x.full
+        copies = ctx.dtype != torch.float32  # whether the products read a rounded copy of the stream
+        if not copies:
+            h = full
+        elif pending is not None:
+            h = pending
+        else:
+            h = norm32_ops.stream_update(full, None, out_dtype=ctx.dtype)
+        y, norm = self.mixer.forward(ctx, h, cache, state), self.mixer_out_norm
+        if self.feed_forward is not None:
+            h = norm32_ops.stream_update(full, y, rms_weight=norm.weight, rms_eps=norm.eps,
+                                         out_dtype=ctx.dtype if copies else None)
+            y, norm = self.feed_forward.forward(ctx, h if copies else full), self.ffn_out_norm
+        nxt = norm32_ops.stream_update(full, y, rms_weight=norm.weight, rms_eps=norm.eps,
+                                       out_dtype=ctx.dtype if (copies and then_norm is not None) else None)
+        return x, nxt
+
+
 @register_part("stream_input", "pass_entry")
 class PassEntry(Part):
     """What enters a 32-bit residual stream where a pass over a run of repeated layers begins:

@@ -53,12 +53,13 @@ class LinearHead(Part):
     """A tied head names the embedding's checkpoint tensor; the loader then hands both parts
     the same device tensor."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, softcap: float | None = None):
+    def __init__(self, vocab_size: int, hidden_size: int, softcap: float | None = None, scale: float = 1.0):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         if softcap is not None and not softcap > 0:
             raise ValueError(f"the cap on the logits must be positive, got {softcap}")
         self.softcap = softcap  # logits <- cap * tanh(logits / cap)
+        self.scale = float(scale)  # logits <- logits * scale (before the cap)
         self.weight = None
 
     def tensor_specs(self):
@@ -69,6 +70,8 @@ class LinearHead(Part):
 
     def forward(self, ctx, h):
         logits = ops.linear(h, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            norm32_ops.scale_(logits, self.scale)
         if self.softcap is not None:
             norm32_ops.softcap_(logits, self.softcap)
         return logits

@@ -52,16 +52,19 @@ class RMSNorm32(Norm):
     product reads); ``scaled_sum`` is the norm of alpha * x + delta, returned as a new
     ``WideStream`` (the arrangement with the norm after the sum)."""
 
-    def __init__(self, hidden_size: int, eps: float):
+    def __init__(self, hidden_size: int, eps: float, unit_offset: bool = False):
         self.hidden_size = hidden_size
         self.eps = eps
+        # True: the gain is stored around zero, y = (1 + w) * x / sqrt(mean(x^2) + eps); 1 + w is formed once, in 32-bit
+        self.unit_offset = bool(unit_offset)
         self.weight = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.hidden_size,), dtype="float32", init="one_plus_normal")}
+        return {"weight": TensorSpec((self.hidden_size,), dtype="float32",
+                                     init="normal" if self.unit_offset else "one_plus_normal")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = (tensors["weight"] + 1.0).contiguous() if self.unit_offset else tensors["weight"]
 
     @staticmethod
     def _full(x):

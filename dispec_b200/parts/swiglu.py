@@ -12,9 +12,11 @@ from dispec_b200.registry import register_part
 
 @register_part("feed_forward", "swiglu")
 class SwiGLUFeedForward(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, out_float32: bool = False):
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
+        # True: the down product returns 32-bit rows (for an arrangement that norms or sums them in 32-bit)
+        self.out_float32 = bool(out_float32)
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self):
@@ -47,4 +49,8 @@ class SwiGLUFeedForward(FeedForward):
             act = gemm_ops.linear_gate_up_swiglu(x, self.w_gate_up)
         else:
             act = ops.swiglu(ops.linear(x, self.w_gate_up), block=self.block)
+        if self.out_float32:
+            if residual is not None or then_norm is not None:
+                raise ValueError("swiglu: 32-bit rows go to an arrangement that does the sum itself")
+            return ops.linear(act, self.w_down, out_dtype=torch.float32)
         return ops.linear(act, self.w_down, residual=residual, out=residual, then_norm=then_norm)

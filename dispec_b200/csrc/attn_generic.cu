@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict__ k_pool,
                     const T* __restrict__ v_pool, const int* __restrict__ page_table,
                     int pt_stride, const int* __restrict__ positions,
-                    const int* __restrict__ seq_of_token, T* __restrict__ out, long out_stride,
+                    const int* __restrict__ seq_of_token, void* __restrict__ out, int out_dtype, long out_stride,
                     int H, int KVH, int D, int Dv, int page_size, int num_pages, int window, int mask_mode,
                     float scale, int sink, const float* __restrict__ sink_values,
                     const float* __restrict__ turn_freq, int* err) {
@@ -160,8 +160,7 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
         if (turn_freq)
           os[g * Dv + d] = acc[g][dd] * inv;
         else
-          out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d] =
-              from_f32<T>(acc[g][dd] * inv);
+          st_any(out, out_dtype, (size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d, acc[g][dd] * inv);
       }
     }
     if (turn_freq) {
@@ -174,7 +173,7 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
         sincosf((float)pos * turn_freq[mth], &sn, &cn);
         // the inverse turn: (u, v) -> (u cos + v sin, v cos - u sin)
         const float v = d < half ? os[i] * cn + os[i + half] * sn : os[i] * cn - os[i - half] * sn;
-        out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d] = from_f32<T>(v);
+        st_any(out, out_dtype, (size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d, v);
       }
     }
   }
@@ -186,7 +185,7 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
                                 const int* positions, const int* seq_of_token, void* out,
                                 long out_stride, int T, int H, int KVH, int D, int Dv, int page_size,
                                 int num_pages, int window, int mask_mode, float scale, int sink,
-                                const float* sink_values, const float* turn_freq, int dtype,
+                                const float* sink_values, const float* turn_freq, int dtype, int out_dtype,
                                 cudaStream_t stream) {
   if (T == 0) return 0;
   DSP_REQUIRE(KVH > 0 && H % KVH == 0, "dsp_attn_generic: H=%d is not a multiple of KVH=%d", H, KVH);
@@ -210,7 +209,7 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
     }
     attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
         (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, page_table, pt_stride,
-        positions, seq_of_token, (float*)out, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
+        positions, seq_of_token, out, out_dtype, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
         mask_mode, scale, sink, sink_values, turn_freq, err);
   } else if (dtype == DSP_BF16) {
     static size_t configured = 0;
@@ -221,7 +220,7 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
     }
     attn_generic_kernel<bf16><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride,
-        positions, seq_of_token, (bf16*)out, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
+        positions, seq_of_token, out, out_dtype, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
         mask_mode, scale, sink, sink_values, turn_freq, err);
   } else {
     DSP_REQUIRE(false, "dsp_attn_generic: unknown dtype %d", dtype);

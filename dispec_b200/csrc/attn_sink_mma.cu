@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128)
 attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restrict__ k_pool,
                      const bf16* __restrict__ v_pool, const int* __restrict__ page_table, int pt_stride,
                      const int* __restrict__ q_start, const int* __restrict__ ctx_len,
-                     const int* __restrict__ tile_seq, const int* __restrict__ tile_tok0, bf16* __restrict__ out,
+                     const int* __restrict__ tile_seq, const int* __restrict__ tile_tok0, void* __restrict__ out, int out_f32,
                      long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, int mask_mode,
                      float scale_log2, int sink, const float* __restrict__ sink_values,
                      const float* __restrict__ turn_freq, int tile_offset, int splits,
@@ -259,7 +259,13 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
           o[i + DV / 16][2 * h + e] = v * cn - u * sn;
         }
     }
-    bf16* dst = out + token * ldo + (size_t)head * DV + (lane & 3) * 2;
+    if (out_f32) {  // 32-bit rows for a consumer that combines heads before it rounds
+      float* dst = reinterpret_cast<float*>(out) + token * ldo + (size_t)head * DV + (lane & 3) * 2;
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      continue;
+    }
+    bf16* dst = reinterpret_cast<bf16*>(out) + token * ldo + (size_t)head * DV + (lane & 3) * 2;
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i)
       *reinterpret_cast<uint32_t*>(dst + i * 8) = pack2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
@@ -274,14 +280,14 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
 extern "C" int DSP_CAT(dsp_attn_sink_mma_k, DSP_DK, _v, DSP_DV)(
     const void* q, long ldq, const void* k_pool, const void* v_pool, const int* page_table, int pt_stride,
     const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0, int tile_offset, int num_tiles,
-    void* out, long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, int mask_mode, float scale,
+    void* out, int out_f32, long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, int mask_mode, float scale,
     int sink, const float* sink_values, const float* turn_freq, int splits, float* part_o, float* part_ml, int* err,
     cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   if (G <= 0 || H % G || tpt <= 0 || tpt * (H / G) > BM || G > 65535 || page_size <= 0 || !err) return 2;
   if (mask_mode < 0 || mask_mode > 1) return 2;
   if (splits < 1 || splits > 32 || (splits > 1 && (!part_o || !part_ml))) return 2;
-  if (((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) || ((uintptr_t)v_pool % 16) || ((uintptr_t)out % 4) || ldq % 8 || ldo % 2)
+  if (((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) || ((uintptr_t)v_pool % 16) || ((uintptr_t)out % (out_f32 ? 8 : 4)) || ldq % 8 || ldo % 2)
     return 3;
   const size_t smem = sizeof(bf16) * ((size_t)BM * LDK + 2 * (size_t)BN * LDK + 2 * (size_t)BN * LDV);
   static bool configured = false;
@@ -292,7 +298,7 @@ extern "C" int DSP_CAT(dsp_attn_sink_mma_k, DSP_DK, _v, DSP_DV)(
   }
   const cudaError_t e = launch_plain(attn_sink_mma_kernel, dim3(num_tiles, G, splits), dim3(128), smem, stream, (const bf16*)q, ldq,
                                      (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride, q_start, ctx_len,
-                                     tile_seq, tile_tok0, (bf16*)out, ldo, H, G, tpt, page_size, num_pages, window,
+                                     tile_seq, tile_tok0, out, out_f32, ldo, H, G, tpt, page_size, num_pages, window,
                                      mask_mode, scale * 1.4426950408889634f, sink, sink_values, turn_freq, tile_offset,
                                      splits, part_o, part_ml, err);
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 1;

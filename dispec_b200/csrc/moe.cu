@@ -44,6 +44,8 @@ __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, 
   return g * (1.f / (1.f + expf(-alpha * g))) * (u + up_shift);
 }
 
+constexpr int GROUPS_PER_LANE = 8;  // the router ranks up to 32 * 8 groups
+
 struct Best {
   float v;
   int i;
@@ -111,7 +113,15 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
   }
   __syncwarp();
   const int per = E / groups;
-  for (int g = lane; g < groups; g += 32) {
+  // Group scores live in registers (lane i: groups i, i + 32, ...), as doubles: the sum of two sigmoids
+  // near 1 (or of two probabilities) is formed from the 32-bit logits in 64-bit, so that groups whose
+  // 32-bit sums would round to the same number are still told apart as exact arithmetic would.
+  double mine[GROUPS_PER_LANE];
+#pragma unroll
+  for (int k = 0; k < GROUPS_PER_LANE; ++k) {
+    const int g = lane + 32 * k;
+    mine[k] = -INFINITY;
+    if (g >= groups) continue;
     float b = -INFINITY, b2 = -INFINITY;  // the group's largest and second largest
     for (int j = 0; j < per; ++j) {
       const float v = sc[g * per + j];
@@ -123,20 +133,38 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
       }
     }
     if (group_kind == 1) {  // the sum of the two largest scores (of the sigmoids, where sc holds logits)
-      const float s1 = score_kind == 1 ? 1.f / (1.f + expf(-b)) : b;
-      const float s2 = per < 2 ? 0.f : score_kind == 1 ? 1.f / (1.f + expf(-b2)) : b2;
-      b = s1 + s2;
+      const double s1 = score_kind == 1 ? 1.0 / (1.0 + exp(-(double)b)) : (double)b;
+      const double s2 = per < 2 ? 0.0 : score_kind == 1 ? 1.0 / (1.0 + exp(-(double)b2)) : (double)b2;
+      mine[k] = s1 + s2;
+    } else {
+      mine[k] = (double)b;
     }
-    gb[g] = b;
   }
-  __syncwarp();
   for (int r = 0; r < keep; ++r) {
-    Best b = {-INFINITY, -1};
-    for (int g = lane; g < groups; g += 32) b = better(b, Best{gb[g], gb[g] > -INFINITY ? g : -1});
-    b = warp_best(b);
-    if (b.i < 0) break;
-    for (int j = lane; j < per; j += 32) ok[b.i * per + j] = 1.f;
-    if (lane == 0) gb[b.i] = -INFINITY;
+    double bv = -INFINITY;
+    int bi = -1;
+#pragma unroll
+    for (int k = 0; k < GROUPS_PER_LANE; ++k) {
+      const int g = lane + 32 * k;
+      if (g < groups && mine[k] > -INFINITY && (bi < 0 || mine[k] > bv)) {  // ascending g: the lower index wins a tie
+        bv = mine[k];
+        bi = g;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (bi < 0) break;
+    for (int j = lane; j < per; j += 32) ok[bi * per + j] = 1.f;
+#pragma unroll
+    for (int k = 0; k < GROUPS_PER_LANE; ++k)
+      if (lane + 32 * k == bi) mine[k] = -INFINITY;
     __syncwarp();
   }
   for (int r = 0; r < top; ++r) {
@@ -429,6 +457,8 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
   if (T == 0) return 0;
   DSP_REQUIRE(score_kind == 0 || score_kind == 1, "dsp_moe_route: unknown score kind %d", score_kind);
   DSP_REQUIRE(h && w && ids && wts, "dsp_moe_route: missing operand");
+  DSP_REQUIRE(groups <= 32 * GROUPS_PER_LANE, "dsp_moe_route: %d groups are more than the router ranks (%d)", groups,
+              32 * GROUPS_PER_LANE);
   DSP_REQUIRE((group_kind == 0 || group_kind == 1) && extra >= 0 && (extra == 0 || extra_out),
               "dsp_moe_route: group kind %d, %d extra rows", group_kind, extra);
   DSP_REQUIRE(E > 0 && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && top > 0 &&

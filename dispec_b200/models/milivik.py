@@ -16,8 +16,8 @@ config.json: ``architecture``, ``vocab``, ``width``, ``embedding.scale``, ``norm
 ``latent_attention``: ``heads``, ``dim``, ``rot_dim``, ``vdim``, ``kv_rank``, ``q_rank``, ``scale``,
 ``mask.size`` (optional), ``rot``: {``dims``, ``base``, ``scaling``: {``factor``, ``original``,
 ``fast``, ``slow``} (optional)} (optional).  ``attention``: ``heads``, ``kv_heads``, ``dim``,
-``vdim``, ``scale``, ``diff``, ``q_temp``: {``coef``, ``every``} (optional), ``mask.size``
-(optional).  ``mlp``: {``kind``: "dense", ``ff``} or {``kind``: "moe", ``expert``: {``ff``},
+``vdim``, ``scale``, ``diff``, ``q_temp``: {``coef``, ``every``} (optional); it sees every
+earlier key.  ``mlp``: {``kind``: "dense", ``ff``} or {``kind``: "moe", ``expert``: {``ff``},
 ``router``: {``experts``, ``top``, ``scale``, ``groups``: {``count``, ``keep``} (optional)},
 ``shared``: {``ff``} (optional)}.  Tensors: ``embed``, ``final.norm`` and, for layer i,
 ``l<i>.norm1|norm2``, ``l<i>.mix.dq|dq.norm|uq|dkv|dkv.norm|uk|uv|g|o`` or
@@ -62,7 +62,7 @@ def _check_mixer(kind: str, m: dict, at: str) -> None:
             _require(m["q_temp"], ["coef", "every"], at + " mixer.q_temp")
             if int(m["q_temp"]["every"]) < 1:
                 raise ConfigError(f"{at}: q_temp.every must be at least 1")
-    if _window(m) < 0:
+    if kind == "latent_attention" and _window(m) < 0:
         raise ConfigError(f"{at}: mask.size must not be negative")
 
 
@@ -160,8 +160,7 @@ def _mixer_spec(cfg: MilivikConfig, kind: str, m: dict, prefix: str) -> PartSpec
     return PartSpec("mixer", "differential_attention",
                     {"hidden_size": h, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "key_dim": m["dim"],
                      "value_dim": m["vdim"], "scale": m["scale"], "diff": m["diff"], "norm_eps": cfg.eps,
-                     "position_encoding": PartSpec("position_encoding", "none"), "window": _window(m),
-                     "q_temp": (qt["coef"], qt["every"]) if qt else None}, names)
+                     "position_encoding": PartSpec("position_encoding", "none"), "q_temp": (qt["coef"], qt["every"]) if qt else None}, names)
 
 
 def _glu_spec(h: int, ff: int, prefix: str) -> PartSpec:

@@ -55,7 +55,7 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor
     dv = v_pool.shape[3]
     assert (kvh, d) == (num_kv_heads, head_dim) and v_pool.shape[:3] == k_pool.shape[:3]
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.dtype == q.dtype == v_pool.dtype
-    assert out.is_contiguous() and out.shape == (T, num_heads * dv) and out.dtype == q.dtype
+    assert out.is_contiguous() and out.shape == (T, num_heads * dv) and out.dtype in (q.dtype, torch.float32)
     assert page_table.dtype == torch.int32 and page_table.stride(1) == 1
     assert positions.dtype == torch.int32 and seq_of_token.dtype == torch.int32
     _check_sink_turn(sink, sink_values, turn_freq, num_heads, dv)
@@ -64,7 +64,7 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor
         page_table.stride(0), L.ptr(positions), L.ptr(seq_of_token), L.ptr(out),
         L.i64(out.stride(0)), T, num_heads, num_kv_heads, head_dim, dv, page_size, num_pages,
         window, int(bool(chunked) and window > 0), L.f32(scale), int(bool(sink)), L.ptr(sink_values),
-        L.ptr(turn_freq), L.dtype_code(q.dtype), L.stream_handle()))
+        L.ptr(turn_freq), L.dtype_code(q.dtype), L.dtype_code(out.dtype), L.stream_handle()))
     return out
 
 
@@ -408,7 +408,7 @@ def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_s
     tokens) is needed where split results are turned back."""
     num_pages, G, page_size, dk = k_pool.shape
     dv = v_pool.shape[3]
-    assert q.dtype == k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16
+    assert q.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and q.stride(1) == 1 and out.stride(1) == 1
     fn = getattr(L.sink_attention_library(dk, dv), f"dsp_attn_sink_mma_k{dk}_v{dv}")
     tpt = SINK_ROWS_PER_TILE // (num_heads // num_kv_heads)
@@ -418,7 +418,7 @@ def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_s
     def launch(offset, count, n_splits, part_o, part_ml):
         rc = fn(L.ptr(q), L.i64(q.stride(0)), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table), page_table.stride(0),
                 L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), offset, count, L.ptr(out),
-                L.i64(out.stride(0)), num_heads, num_kv_heads, tpt, page_size, num_pages, window, mask_mode,
+                int(out.dtype == torch.float32), L.i64(out.stride(0)), num_heads, num_kv_heads, tpt, page_size, num_pages, window, mask_mode,
                 L.f32(scale), int(bool(sink)), L.ptr(sink_values), L.ptr(turn_freq), n_splits, L.ptr(part_o), L.ptr(part_ml), ctypes.c_void_p(_device_error_address(q.device)),
                 L.stream_handle())
         L.LaunchCounter.n += 1
@@ -448,7 +448,8 @@ def sink_paged_attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, num_hea
                          key_dim: int, value_dim: int, window: int, scale: float, sink: bool, chunked: bool = False,
                          sink_values: torch.Tensor | None = None, turn_freq: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of the step over pools whose keys and values have widths of their own, with an
-    optional sink in the softmax: q [T, H * Dk] (already turned), out [T, H * Dv].  bfloat16 runs
+    optional sink in the softmax: q [T, H * Dk] (already turned), out [T, H * Dv] (of q's type, or
+    float32 for a consumer that combines heads before it rounds).  bfloat16 runs
     on the tensor-core kernel where it is built for the sizes and the batch lists its tiles;
     everything else (and float32 always) on the 32-bit kernel.  ``chunked``: ``window`` is the
     size of the chunks a position's keys come from; ``sink_values``: the sink's score per head;

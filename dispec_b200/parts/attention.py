@@ -314,7 +314,9 @@ class DifferentialAttention(Mixer):
         q = attn_ops.qkv_rotate_store(z[:, :n_qkv], ctx.positions, ctx.seq_of_token, cache, inv_freq, rotary_dim, H, G,
                                       dk, dv, ctx.dtype, q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.norm_eps,
                                       maps=2, q_temp=self.q_temp)
-        maps = torch.empty((q.shape[0], 2 * H * dv), dtype=q.dtype, device=q.device)
+        # the maps stay 32-bit: their difference is divided by its own root mean square, which would
+        # magnify a rounding of the two
+        maps = torch.empty((q.shape[0], 2 * H * dv), dtype=torch.float32, device=q.device)
         attn_ops.sink_paged_attention(ctx, q, cache, maps, 2 * H, G, 2 * dk, dv, self.window,
                                       self.scale * self.position_encoding.score_scale(), False)
         heads = norm32_ops.diff_heads(maps, H, self.lam, 1.0 - self.diff, self.norm_eps, ctx.dtype,

@@ -10,7 +10,7 @@ import math
 import torch
 
 F = torch.float64
-ROUTING_MARGINS = None  # a list: moe() appends, per token, the gap between the last chosen and the next score
+ROUTING_MARGINS = None  # a list: route() appends (token, how far its choice of groups and experts was from another one)
 
 
 def rms(x, eps):
@@ -128,9 +128,10 @@ def diff_lambda(W, p, diff):
     return math.exp(float((W[p + "lq1"] * W[p + "lk1"]).sum())) - math.exp(float((W[p + "lq2"] * W[p + "lk2"]).sum())) + diff
 
 
-def diff_attention(h, W, p, m, eps, pos, past=None):
+def diff_attention(h, W, p, m, eps, pos, past=None, window=0):
     """Two softmax maps over the same values, o = a1 - lambda a2, each head divided by its root mean
-    square and scaled by 1 - diff, a gate per head.  ``past`` = (k, v, positions)."""
+    square and scaled by 1 - diff, a gate per head.  ``past`` = (k, v, positions).  Every earlier key
+    is seen (the design has no window here; ``window`` serves tests of a mixer that is given one)."""
     T = h.shape[0]
     H, G, d, dv, diff = m["heads"], m["kv_heads"], m["dim"], m["vdim"], float(m["diff"])
     q = norm_plain((h @ W[p + "q"].T).view(T, H, 2, d), W[p + "q.norm"], eps)
@@ -144,8 +145,8 @@ def diff_attention(h, W, p, m, eps, pos, past=None):
     group = H // G
     kk = k.repeat_interleave(group, dim=1)  # query head a uses key/value head a // group
     vv = v.repeat_interleave(group, dim=1)
-    a1 = softmax_attention(q[:, :, 0], kk[:, :, 0], vv, pos, pos_k, m["scale"], 0)
-    a2 = softmax_attention(q[:, :, 1], kk[:, :, 1], vv, pos, pos_k, m["scale"], 0)
+    a1 = softmax_attention(q[:, :, 0], kk[:, :, 0], vv, pos, pos_k, m["scale"], window)
+    a2 = softmax_attention(q[:, :, 1], kk[:, :, 1], vv, pos, pos_k, m["scale"], window)
     o = rms(a1 - diff_lambda(W, p, diff) * a2, eps) * (1.0 - diff)
     o = o * torch.sigmoid(h @ W[p + "g"].T)[:, :, None]
     return o.reshape(T, H * dv) @ W[p + "o"].T, (k, v, pos_k)
@@ -174,7 +175,7 @@ def route(h, W, p, r):
         gap = (best.values[:, top - 1] - best.values[:, top]) if E > top else torch.full((T,), 1.0, dtype=F)
         gsort = gs.sort(-1, descending=True).values
         ggap = (gsort[:, keep - 1] - gsort[:, keep]) if n > keep else torch.full((T,), 1.0, dtype=F)
-        ROUTING_MARGINS.extend(torch.minimum(gap, ggap).tolist())
+        ROUTING_MARGINS.extend(enumerate(torch.minimum(gap, ggap).tolist()))
     ids, w = best.indices[:, :top], best.values[:, :top]
     return ids, w / (w.sum(-1, keepdim=True) + 1e-20) * float(r.get("scale", 1.0))
 

@@ -864,6 +864,137 @@ def desalix_points(args, pk: dict) -> dict:
             print(f"bench: {key} done", file=sys.stderr, flush=True)
     return out
 
+# ------------------------------------------------------------ Milivik beside Desalix at equal size
+# Milivik's closest relative in this package is Desalix (softmax attention over a bounded span of
+# keys, mixtures of gated experts with sigmoid scores and a shared expert, norms around the
+# sublayers on a 32-bit residual stream).  Both with eight layers at the same width, heads,
+# vocabulary, span (windows of 1,024 keys against chunks of 1,024 positions), number of experts
+# and feed-forward weights a token passes (16 experts of a quarter of the dense width of which 2
+# are used, a shared expert of half of it).  Milivik: latent attention + dense, two-map attention
+# + experts, latent attention + experts twice; that period twice.  The two-map attention has the
+# heads' width split over its two maps, so that its keys are as wide as Desalix's.
+MILIVIK_LAYERS = 8
+
+
+def milivik_config(shape: str) -> dict:
+    z, lat = MURUTAR_SHAPES[shape], PULUDRA_SHAPES[shape]
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["groups"], "keep": z["keep"]}},
+           "shared": {"ff": z["ff"] // 2}}
+    latent = {"heads": lat["heads"], "dim": lat["dim"], "rot_dim": lat["rot_dim"], "vdim": lat["vdim"],
+              "kv_rank": lat["kv_rank"], "q_rank": lat["q_rank"], "scale": (lat["dim"] + lat["rot_dim"]) ** -0.5,
+              "mask": {"size": z["window"]},
+              "rot": {"base": 1e6, "dims": lat["rot_dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    maps = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"] // 2, "vdim": z["vdim"], "diff": 0.3,
+            "scale": (z["dim"] // 2) ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+    period = [{"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": z["ff"]}},
+              {"type": "attention", "mixer": maps, "mlp": moe},
+              {"type": "latent_attention", "mixer": latent, "mlp": moe},
+              {"type": "latent_attention", "mixer": latent, "mlp": moe}]
+    return {"architecture": "Milivik", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": period * (MILIVIK_LAYERS // 4)}
+
+
+def desalix_flat_config(shape: str, layers: int) -> dict:
+    cfg = desalix_config(shape)
+    cfg.pop("loop")
+    cfg["layers"] = cfg["layers"][:1] * layers
+    return cfg
+
+
+def milivik_bytes_and_flops(cfg: dict):
+    """As ``murutar_bytes_and_flops``.  Latent attention is counted as it runs (the key map folded
+    into the queries, the value map applied to the result: keys of width kv_rank + rot_dim and values
+    of width kv_rank for every head); the two-map attention by its two maps of ``dim`` and their
+    shared values, not by the zero halves of the query rows."""
+    W, V = cfg["width"], cfg["vocab"]
+    fixed, cache_layers, attn, expert_layers = 0, [], [], []
+    for e in cfg["layers"]:
+        m, mlp = e["mixer"], e.get("mlp")
+        if e["type"] == "latent_attention":
+            H, d, r, dv, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            win = (m.get("mask") or {}).get("size", 0)
+            n = (Q + R + r + H * dv) * W + H * (d + r) * Q + H * d * R + H * dv * R + W * H * dv
+            cache_layers.append(((R + r) * 2, win))
+            attn.append((H * (2 * R + r), win))
+        else:
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            n = (H * 2 * d + G * 2 * d + G * dv + H) * W + W * H * dv
+            cache_layers.append((G * (2 * d + dv) * 2, 0))
+            attn.append((2 * H * (d + dv), 0))
+        if mlp is not None and mlp["kind"] == "dense":
+            n += 3 * mlp["ff"] * W
+        elif mlp is not None:
+            r_ = mlp["router"]
+            n += (r_["experts"] + 1) * W * 2 + 3 * (mlp.get("shared") or {"ff": 0})["ff"] * W  # float32 router and gate row
+            expert_layers.append((r_["experts"], r_["top"], 3 * mlp["expert"]["ff"] * W))
+        fixed += n
+
+    def weight_bytes(batch):
+        return 2 * (fixed + V * W + sum(min(E, batch * top) * w for E, top, w in expert_layers))
+
+    def cache_bytes(ctx):
+        return sum(per * (min(ctx, win) if win else ctx) for per, win in cache_layers)
+
+    def prefill_flops(T):
+        f = 2 * T * (fixed + sum(top * w for _, top, w in expert_layers)) + 2 * V * W
+        for per, win in attn:
+            keys = sum(min(t + 1, win) if win else t + 1 for t in range(T))
+            f += 2 * per * keys
+        return f
+
+    total = 2 * (fixed + V * W + sum(E * w for E, _, w in expert_layers))
+    return weight_bytes, cache_bytes, 0, prefill_flops, total
+
+
+def milivik_points(args, pk: dict) -> dict:
+    """Prefill (2,048 tokens in one step) and decode (batch 1, 8, 64 from captured graphs, 1,536
+    tokens into the sequence) of Milivik and of Desalix with as many layers, at equal sizes, each
+    with the fraction of its own roofline."""
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner
+    from dispec_b200.weights import load_random_model
+    prompt_len = PROMPT_LEN + PROMPT_LEN // 2
+    out = {"only": "milivik", "layers": MILIVIK_LAYERS, "prompt_len": prompt_len, "prefill_tokens": PREFILL_TOKENS, "peaks": pk}
+    steps, warmup = max(20, min(args.steps, 50)), max(3, args.warmup // 2)
+    per_req = (prompt_len + NEW_TOKENS + steps + warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    shapes = ["1.5b"] if args.no_other_shapes else list(MURUTAR_SHAPES)
+    for shape in shapes:
+        for family in ("milivik", "desalix"):
+            if family == "milivik":
+                cfg_dict = milivik_config(shape)
+                weight_bytes, cache_bytes, state_bytes, prefill_flops, total = milivik_bytes_and_flops(cfg_dict)
+            else:
+                cfg_dict = desalix_flat_config(shape, MILIVIK_LAYERS)
+                weight_bytes, cache_bytes, state_bytes, prefill_flops, total = desalix_bytes_and_flops(cfg_dict)
+            vocab = cfg_dict["vocab"]
+            model = load_random_model(load_model_config(cfg_dict), 5, STD, "bfloat16", "cuda:0")
+            torch.cuda.synchronize()
+            key = f"{family}_{shape}"
+            out[f"{key}_weight_gb"] = round(total / 1e9, 3)
+            for b in (1, 8, 64):
+                r = ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(b * per_req, 160), max_num_seqs=max(b, 8),
+                                cuda_graph=True)
+                ms, launches, ctx = decode_direct(r, random_prompts(b, prompt_len, vocab, 13 + b), steps, warmup)
+                step_bytes = weight_bytes(b) + b * (cache_bytes(ctx) + state_bytes)
+                out[f"{key}_decode_b{b}"] = round(b * 1000.0 / ms, 1)
+                out[f"{key}_decode_b{b}_ms"] = round(ms, 4)
+                out[f"{key}_decode_b{b}_hbm_frac"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                out[f"{key}_decode_b{b}_launches_per_step"] = launches // steps
+                print(f"bench: {key} decode at batch {b}: {ms:.3f} ms a step", file=sys.stderr, flush=True)
+                if b == 1:
+                    pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=3)
+                    out[f"{key}_prefill"] = round(PREFILL_TOKENS / pms * 1000.0, 1)
+                    out[f"{key}_prefill_ms"] = round(pms, 3)
+                    out[f"{key}_prefill_frac"] = round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+                del r
+                torch.cuda.empty_cache()
+            del model
+            torch.cuda.empty_cache()
+            print(f"bench: {key} done", file=sys.stderr, flush=True)
+    return out
+
 
 def run_ours(args) -> dict:
     import torch
@@ -885,6 +1016,8 @@ def run_ours(args) -> dict:
         return murutar_points(args, peaks())
     if args.only == "desalix":
         return desalix_points(args, peaks())
+    if args.only == "milivik":
+        return milivik_points(args, peaks())
     cfg_dict = dict(BENCH_CONFIG)
     seed = SEED
     if args.shape != "1.5b":
@@ -1054,7 +1187,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra", "murutar", "desalix"],
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra", "murutar", "desalix", "milivik"],
                     default=None,
                     help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
                          "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
@@ -1063,7 +1196,7 @@ def main() -> int:
                          "alone, by shape, length and the order of the pages; puludra: prefill and decode of the Puludra design beside "
                          "Qwen2 at equal width, depth, vocabulary and feed-forward width (eight layers each), with roofline fractions; "
                          "murutar: the same for the Murutar design beside Puludra; desalix: the same for the Desalix design beside "
-                         "Murutar with attention and experts in every layer")
+                         "Murutar with attention and experts in every layer; milivik: the same for the Milivik design beside Desalix")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")

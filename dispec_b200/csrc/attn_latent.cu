@@ -695,6 +695,8 @@ extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, in
 // applying the value map to the attention's result (A_h: sum_j p_j c_j, W_h = Wv_h).  A_h and C_h
 // are column blocks of row-major matrices (row strides lda / ldc, head strides a_hs / c_hs);
 // W is [H, N, K] contiguous.  64 x 64 tiles, k in steps of 32, cp.async in two buffers, mma.sync.
+// With `gate` (a row-major matrix laid out like C's columns) every result is multiplied by the
+// sigmoid of its gate value before it is stored: an output gate on the heads.
 namespace hp {
 constexpr int BM = 64, BN = 64, BK = 32, THREADS = 128, ROWB = 80;
 
@@ -703,6 +705,7 @@ struct Args {
   const bf16* W;
   void* C; int c_dtype; long ldc, c_hs;
   int M, N, K;
+  const void* gate; int g_dtype; long ldg;  // optional: C[m, h, n] *= sigmoid(gate[m * ldg + h * c_hs + n])
 };
 
 __global__ void __launch_bounds__(THREADS) head_products_kernel(const Args p) {
@@ -771,13 +774,18 @@ __global__ void __launch_bounds__(THREADS) head_products_kernel(const Args p) {
       for (int e = 0; e < 4; ++e) {
         const int row = m0 + wm * 32 + i * 16 + g + (e >> 1) * 8;
         const int col = n0 + wn * 32 + j * 8 + 2 * c4 + (e & 1);
-        if (row < p.M && col < p.N) st_any(p.C, p.c_dtype, (size_t)row * p.ldc + (size_t)z * p.c_hs + col, acc[i][j][e]);
+        if (row < p.M && col < p.N) {
+          float v = acc[i][j][e];
+          if (p.gate) v /= 1.f + expf(-ld_any(p.gate, p.g_dtype, (size_t)row * p.ldg + (size_t)z * p.c_hs + col));
+          st_any(p.C, p.c_dtype, (size_t)row * p.ldc + (size_t)z * p.c_hs + col, v);
+        }
       }
 }
 }  // namespace hp
 
 extern "C" int dsp_head_products(const void* A, long lda, long a_hs, const void* W, void* C, int c_dtype,
-                                 long ldc, long c_hs, int M, int N, int K, int H, cudaStream_t stream) {
+                                 long ldc, long c_hs, int M, int N, int K, int H, const void* gate, int g_dtype,
+                                 long ldg, cudaStream_t stream) {
   if (M == 0 || N == 0 || H == 0) return 0;
   DSP_REQUIRE(A && W && C && K > 0 && K % hp::BK == 0, "dsp_head_products: K=%d must be a positive multiple of %d", K, hp::BK);
   DSP_REQUIRE(lda % 8 == 0 && a_hs % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((long)N * K) % 8 == 0,
@@ -786,6 +794,7 @@ extern "C" int dsp_head_products(const void* A, long lda, long a_hs, const void*
   hp::Args a;
   a.A = (const bf16*)A; a.lda = lda; a.a_hs = a_hs; a.W = (const bf16*)W;
   a.C = C; a.c_dtype = c_dtype; a.ldc = ldc; a.c_hs = c_hs; a.M = M; a.N = N; a.K = K;
+  a.gate = gate; a.g_dtype = g_dtype; a.ldg = ldg;
   DSP_CUDA(launch_plain(hp::head_products_kernel, dim3((N + hp::BN - 1) / hp::BN, (M + hp::BM - 1) / hp::BM, H),
                         dim3(hp::THREADS), 0, stream, a));
   DSP_CHECK_LAUNCH("dsp_head_products");

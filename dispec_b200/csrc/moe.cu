@@ -29,6 +29,8 @@
 //                    64 pairs (1) or 128 pairs (2); the plan must have been made for tiles of that many rows.
 //   dsp_moe_combine  y[t] = base[t] * base_scale[t] + sum_k weight[t, k] * P[t * top + k], in ascending k
 //                    (without `base`: from 0; without `base_scale`: 1; without `weight`: every weight 1).
+#include <climits>
+
 #include "common.cuh"
 
 namespace {
@@ -113,14 +115,18 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
   }
   __syncwarp();
   const int per = E / groups;
-  // Group scores live in registers (lane i: groups i, i + 32, ...), as doubles: the sum of two sigmoids
-  // near 1 (or of two probabilities) is formed from the 32-bit logits in 64-bit, so that groups whose
-  // 32-bit sums would round to the same number are still told apart as exact arithmetic would.
-  double mine[GROUPS_PER_LANE];
+  // Group scores live in registers (lane i: groups i, i + 32, ...) as a whole number plus a small
+  // part: a sigmoid above one half is kept as 1 - sigmoid(-z), so that the sum of two scores near 1 is
+  // 2 minus two small deficits that float arithmetic holds exactly enough to rank groups whose plain
+  // 32-bit sums would all round to 2 (a saturated router would otherwise send every token to the
+  // first groups).  Group a beats group b when (a.whole - b.whole) + (a.part - b.part) > 0.
+  int whole[GROUPS_PER_LANE];
+  float part[GROUPS_PER_LANE];
 #pragma unroll
   for (int k = 0; k < GROUPS_PER_LANE; ++k) {
     const int g = lane + 32 * k;
-    mine[k] = -INFINITY;
+    whole[k] = INT_MIN;  // no group, or one that is open already
+    part[k] = 0.f;
     if (g >= groups) continue;
     float b = -INFINITY, b2 = -INFINITY;  // the group's largest and second largest
     for (int j = 0; j < per; ++j) {
@@ -132,39 +138,54 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
         b2 = fmaxf(b2, v);
       }
     }
-    if (group_kind == 1) {  // the sum of the two largest scores (of the sigmoids, where sc holds logits)
-      const double s1 = score_kind == 1 ? 1.0 / (1.0 + exp(-(double)b)) : (double)b;
-      const double s2 = per < 2 ? 0.0 : score_kind == 1 ? 1.0 / (1.0 + exp(-(double)b2)) : (double)b2;
-      mine[k] = s1 + s2;
+    whole[k] = 0;
+    if (group_kind == 1 && score_kind == 1) {  // the sum of the two largest sigmoids (sc holds logits)
+      const int n = per < 2 ? 1 : 2;
+      for (int i = 0; i < n; ++i) {
+        const float z = i ? b2 : b;
+        const float small = 1.f / (1.f + expf(fabsf(z)));  // sigmoid(-|z|)
+        whole[k] += z > 0.f;
+        part[k] += z > 0.f ? -small : small;
+      }
+    } else if (group_kind == 1) {
+      part[k] = b + (per < 2 ? 0.f : b2);
     } else {
-      mine[k] = (double)b;
+      part[k] = b;
     }
   }
+  auto beats = [](int wa, float pa, int ia, int wb, float pb, int ib) {
+    if (wa == INT_MIN) return false;
+    if (wb == INT_MIN) return true;
+    const float d = (float)(wa - wb) + (pa - pb);
+    return d > 0.f || (d == 0.f && ia < ib);
+  };
   for (int r = 0; r < keep; ++r) {
-    double bv = -INFINITY;
-    int bi = -1;
+    int bw = INT_MIN, bi = -1;
+    float bp = 0.f;
 #pragma unroll
     for (int k = 0; k < GROUPS_PER_LANE; ++k) {
       const int g = lane + 32 * k;
-      if (g < groups && mine[k] > -INFINITY && (bi < 0 || mine[k] > bv)) {  // ascending g: the lower index wins a tie
-        bv = mine[k];
+      if (g < groups && beats(whole[k], part[k], g, bw, bp, bi)) {
+        bw = whole[k];
+        bp = part[k];
         bi = g;
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) {
-        bv = ov;
+      const int ow = __shfl_xor_sync(0xffffffffu, bw, o), oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+      if (beats(ow, op, oi, bw, bp, bi)) {
+        bw = ow;
+        bp = op;
         bi = oi;
       }
     }
-    if (bi < 0) break;
+    if (bw == INT_MIN) break;
     for (int j = lane; j < per; j += 32) ok[bi * per + j] = 1.f;
 #pragma unroll
     for (int k = 0; k < GROUPS_PER_LANE; ++k)
-      if (lane + 32 * k == bi) mine[k] = -INFINITY;
+      if (lane + 32 * k == bi) whole[k] = INT_MIN;
     __syncwarp();
   }
   for (int r = 0; r < top; ++r) {

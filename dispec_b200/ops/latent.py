@@ -154,14 +154,20 @@ def head_products_supported(x: torch.Tensor, head_stride: int, w: torch.Tensor) 
             and (w.shape[1] * w.shape[2]) % 8 == 0 and w.is_contiguous())
 
 
-def head_products(x: torch.Tensor, head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int) -> torch.Tensor:
+def head_products(x: torch.Tensor, head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
+                  gate: torch.Tensor | None = None) -> torch.Tensor:
     """out[:, h * out_head_stride : + N] = x[:, h * head_stride : + K] @ w[h].T for every head h of
     ``w`` [H, N, K] in one launch (bfloat16 operands, 32-bit accumulation; ``out`` float32 or
-    bfloat16, any column offset baked into the tensors handed in)."""
+    bfloat16, any column offset baked into the tensors handed in).  ``gate`` (a matrix whose columns
+    are laid out like ``out``'s): every result is multiplied by the sigmoid of its gate value."""
     assert head_products_supported(x, head_stride, w) and out.stride(1) == 1 and out.is_cuda
     H, N, K = w.shape
     lib = L.mixer_library("attn_latent")
+    if gate is not None:
+        assert gate.is_cuda and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[0] == x.shape[0]
+        assert gate.shape[1] >= (H - 1) * out_head_stride + N
     L.check(lib.dsp_head_products(L.ptr(x), L.i64(x.stride(0)), L.i64(head_stride), L.ptr(w), L.ptr(out),
                                   L.dtype_code(out.dtype), L.i64(out.stride(0)), L.i64(out_head_stride), x.shape[0],
-                                  N, K, H, L.stream_handle()))
+                                  N, K, H, L.ptr(gate), L.dtype_code(gate.dtype) if gate is not None else 0,
+                                  L.i64(gate.stride(0) if gate is not None else 0), L.stream_handle()))
     return out

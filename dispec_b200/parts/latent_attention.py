@@ -104,11 +104,12 @@ class LatentAttention(Mixer):
                                                 ctx.positions, ctx.seq_of_token, H, scale, x.dtype,
                                                 window=self.window, **turn)
         heads = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
+        gate = down[:, Q + R + r:] if self.gate else None
         if latent_ops.head_products_supported(mixed, R, self.w_uv):
-            latent_ops.head_products(mixed, R, self.w_uv, heads, dv)
+            latent_ops.head_products(mixed, R, self.w_uv, heads, dv, gate=gate)  # the gate rides in the epilogue
         else:
             for a in range(H):
                 ops.linear(mixed[:, a * R:(a + 1) * R], self.w_uv[a], out=heads[:, a * dv:(a + 1) * dv])
-        if self.gate:
-            heads = norm32_ops.sigmoid_gate(heads, down[:, Q + R + r:], x.dtype)
+            if gate is not None:
+                heads = norm32_ops.sigmoid_gate(heads, gate, x.dtype)
         return ops.linear(heads, self.w_o, out_dtype=torch.float32)

@@ -45,7 +45,7 @@ class RotaryEncoding(PositionEncoding):
         self.slowed = None
         if slowed is not None:
             factor, original, fast, slow = (float(v) for v in slowed)
-            if not (factor >= 1.0 and original > 0 and fast > 0 and slow > 0 and self.theta > 1.0):
+            if not (factor > 0.0 and original > 0 and fast > 0 and slow > 0 and self.theta > 0.0 and self.theta != 1.0):
                 raise ValueError(f"slowed rotation: factor={factor} original={original} fast={fast} slow={slow} "
                                  f"theta={self.theta} do not describe one")
             self.slowed = (factor, original, fast, slow)

@@ -89,7 +89,7 @@ def test_part_constructors_refuse_what_cannot_run():
     with pytest.raises(ValueError):
         GatedMoE(16, 8, 6, top=2, limit=None, shared_gate=True)
     with pytest.raises(ValueError):
-        RotaryEncoding(16, 10000.0, slowed=(0.5, 64, 16, 1))
+        RotaryEncoding(16, 10000.0, slowed=(0.0, 64, 16, 1))
 
 
 @pytest.mark.parametrize("dims,base,slowed", [(8, 10000.0, (4.0, 64, 16.0, 2.0)), (6, 300.0, (1.5, 20, 4.0, 1.0)),

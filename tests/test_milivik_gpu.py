@@ -620,6 +620,19 @@ def test_latent_attention_on_tensor_cores_with_a_window(H, R, r, page, window):
         assert (out[t] - want).abs().max() < 0.05 * max(1.0, want.abs().max().item()), (t, star[t], pos[t])
 
 
+def test_head_products_kernel_with_an_output_gate():
+    from dispec_b200.ops import latent as LO
+    g = torch.Generator().manual_seed(9)
+    M, H, N, K = 70, 5, 48, 64
+    x = torch.randn(M, H * K, generator=g).bfloat16()
+    w = (torch.randn(H, N, K, generator=g) / K ** 0.5).bfloat16()
+    gate = torch.randn(M, 7 + H * N, generator=g)
+    out = torch.full((M, H * N), float("nan"), dtype=torch.float32, device="cuda:0")
+    LO.head_products(x.cuda(), K, w.cuda(), out, N, gate=dev(gate)[:, 7:])
+    want = torch.einsum("mhk,hnk->mhn", x.double().view(M, H, K), w.double()).reshape(M, H * N) * torch.sigmoid(gate[:, 7:].double())
+    assert (out.cpu().double() - want).abs().max() < 1e-4 * max(1.0, want.abs().max().item())
+
+
 # ----------------------------------------------------------------------- the two-map attention part
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dk,dv,page,window", [(4, 2, 16, 32, 16, 0), (5, 5, 6, 10, 8, 21), (8, 2, 64, 128, 16, 0),

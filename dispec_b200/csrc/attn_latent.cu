@@ -12,7 +12,9 @@
 // which is attention with ONE key/value head of key width R + r and value width R.
 //
 // latent_store_kernel: RMS norm (32-bit) of the first R columns of the down projection with a
-// gain, rotation of the last r columns, both written to the token's place in the pages.
+// gain, rotation of the last r columns, both written to the token's place in the pages.  With
+// `cq_out` it also writes the RMS norm of the query latent (columns q_off .. q_off + Qn, gain
+// `q_gain`) of every row, padding rows included: the same block has the row at hand.
 // The rotation turns pair i of the first `rot` of the r dimensions by the angle
 // position * inv_freq[i]; the rest pass unchanged.  `layout` 0: pair i = (2i, 2i+1) (interleaved);
 // 1: pair i = (i, i + rot/2) (halves).  Cosine and sine are multiplied by `mag` (a rotation that also
@@ -46,10 +48,23 @@ latent_store_kernel(const void* __restrict__ down, int d_dtype, long ldd, int c_
                     int rot, int layout, float mag, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                     const int* __restrict__ page_table, int pt_stride, void* __restrict__ c_pool,
                     void* __restrict__ r_pool, int pool_dtype, int R, int r, int page_size,
-                    int num_pages, int* err) {
+                    int num_pages, int q_off, int Qn, const float* __restrict__ q_gain,
+                    void* __restrict__ cq_out, int cq_dtype, long ld_cq, int* err) {
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int pos = positions[t];
+  if (cq_out) {
+    const size_t qrow = (size_t)t * ldd + q_off;
+    float qs = 0.f;
+    for (int i = threadIdx.x; i < Qn; i += THREADS) {
+      const float v = ld_any(down, d_dtype, qrow + i);
+      qs = fmaf(v, v, qs);
+    }
+    const float qinv = 1.f / sqrtf(block_sum(qs, scratch) / (float)Qn + eps);
+    for (int i = threadIdx.x; i < Qn; i += THREADS)
+      st_any(cq_out, cq_dtype, (size_t)t * ld_cq + i, ld_any(down, d_dtype, qrow + i) * qinv * q_gain[i]);
+    __syncthreads();  // the scratch of the sum is used again below
+  }
   if (pos < 0) return;
   const int page = page_table[(size_t)seq_of_token[t] * pt_stride + pos / page_size];
   if (page < 0 || page >= num_pages) {
@@ -256,16 +271,19 @@ extern "C" int dsp_latent_store(const void* down, int d_dtype, long ldd, int c_o
                                 const float* gain, float eps, const float* inv_freq, int rot, int layout,
                                 float mag, const int* positions, const int* seq_of_token, const int* page_table,
                                 int pt_stride, void* c_pool, void* r_pool, int pool_dtype, int T_, int R,
-                                int r, int page_size, int num_pages, cudaStream_t stream) {
+                                int r, int page_size, int num_pages, int q_off, int Qn, const float* q_gain,
+                                void* cq_out, int cq_dtype, long ld_cq, cudaStream_t stream) {
   if (T_ == 0) return 0;
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_latent_store: no device error word");
   DSP_REQUIRE(down && gain && c_pool && r_pool && R > 0 && r >= 0, "dsp_latent_store: missing operand");
   DSP_REQUIRE(rot >= 0 && rot <= r && rot % 2 == 0 && (rot == 0 || inv_freq), "dsp_latent_store: rot=%d of %d", rot, r);
   DSP_REQUIRE(layout == 0 || layout == 1, "dsp_latent_store: unknown layout %d", layout);
+  DSP_REQUIRE(!cq_out || (q_gain && Qn > 0 && q_off >= 0), "dsp_latent_store: a query latent without gain or size");
   DSP_CUDA(launch_plain(latent_store_kernel, dim3(T_), dim3(THREADS), 0, stream, down, d_dtype, ldd, c_off,
                       r_off, gain, eps, inv_freq, rot, layout, mag, positions, seq_of_token, page_table, pt_stride,
-                      c_pool, r_pool, pool_dtype, R, r, page_size, num_pages, err));
+                      c_pool, r_pool, pool_dtype, R, r, page_size, num_pages, q_off, Qn, q_gain, cq_out, cq_dtype,
+                      ld_cq, err));
   DSP_CHECK_LAUNCH("dsp_latent_store");
   return 0;
 }

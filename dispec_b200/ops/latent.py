@@ -15,12 +15,14 @@ _LAYOUTS = {"interleaved": 0, "halves": 1}  # which dimensions form pair i: (2i,
 def latent_store(down: torch.Tensor, c_off: int, r_off: int, gain: torch.Tensor, eps: float,
                  inv_freq: torch.Tensor | None, rot: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
                  page_table: torch.Tensor, c_pool: torch.Tensor, r_pool: torch.Tensor,
-                 layout: str = "interleaved", magnitude: float = 1.0) -> None:
+                 layout: str = "interleaved", magnitude: float = 1.0, query_latent: tuple | None = None):
     """``down`` [T, columns]: rows of the down projection; columns c_off.. hold the R latent values
     (RMS-normed here with ``gain``), columns r_off.. the r values of the shared key part (pair i
     of its first ``rot`` values, (2i, 2i+1) or with ``layout`` "halves" (i, i + rot/2), turned by
     position * inv_freq[i], cosine and sine times ``magnitude``).  Pools:
-    [num_pages, 1, page_size, R] and [num_pages, 1, page_size, r]."""
+    [num_pages, 1, page_size, R] and [num_pages, 1, page_size, r].
+    ``query_latent`` = (offset, size, gain, out_dtype): the same launch also returns the RMS norm
+    (same eps) of columns offset .. offset + size of every row times ``gain``, [T, size]."""
     if not (down.is_cuda and c_pool.is_cuda):
         raise L.KernelError("latent_store: CUDA tensors only (there is no CPU path)")
     assert down.dim() == 2 and down.stride(1) == 1
@@ -33,13 +35,21 @@ def latent_store(down: torch.Tensor, c_off: int, r_off: int, gain: torch.Tensor,
     assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
     if rot:
         assert inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.shape[0] >= rot // 2
+    cq, q_off, Qn, q_gain = None, 0, 0, None
+    if query_latent is not None:
+        q_off, Qn, q_gain, cq_dtype = query_latent
+        assert q_gain.dtype == torch.float32 and q_gain.shape == (Qn,) and q_gain.is_contiguous()
+        assert 0 <= q_off and q_off + Qn <= down.shape[1]
+        cq = torch.empty((down.shape[0], Qn), dtype=cq_dtype, device=down.device)
     lib = L.mixer_library("attn_latent")
     L.check(lib.dsp_latent_store(
         L.ptr(down), L.dtype_code(down.dtype), L.i64(down.stride(0)), c_off, r_off, L.ptr(gain), L.f32(eps),
         L.ptr(inv_freq), rot, _LAYOUTS[layout], L.f32(magnitude), L.ptr(positions), L.ptr(seq_of_token),
         L.ptr(page_table), page_table.stride(0),
         L.ptr(c_pool), L.ptr(r_pool), L.dtype_code(c_pool.dtype), down.shape[0], R, r, page_size, num_pages,
-        L.stream_handle()))
+        q_off, Qn, L.ptr(q_gain), L.ptr(cq), L.dtype_code(cq.dtype) if cq is not None else 0,
+        L.i64(cq.stride(0) if cq is not None else 0), L.stream_handle()))
+    return cq
 
 
 def latent_attention(q_absorbed: torch.Tensor, q: torch.Tensor, q_head_stride: int, qr_off: int,

@@ -84,10 +84,12 @@ class LatentAttention(Mixer):
         scale = self.scale * self.position_encoding.score_scale()
         down = ops.linear(x, self.w_down, out_dtype=torch.float32)  # [T, Q | R | r]
         c_pool, r_pool = cache.tensors["latent"], cache.tensors["rotated_key"]
-        if cache.write:
-            latent_ops.latent_store(down, Q, Q + R, self.c_gain, self.eps, inv_freq, rot_n, ctx.positions,
-                                    ctx.seq_of_token, cache.page_table, c_pool, r_pool, **turn)
-        cq = norm32_ops.sum_norm(down[:, :Q], self.q_gain, self.eps, out_dtype=x.dtype, want32=False)[1]
+        if cache.write:  # the store's block has the row at hand: it norms the query latent as well
+            cq = latent_ops.latent_store(down, Q, Q + R, self.c_gain, self.eps, inv_freq, rot_n, ctx.positions,
+                                         ctx.seq_of_token, cache.page_table, c_pool, r_pool,
+                                         query_latent=(0, Q, self.q_gain, x.dtype), **turn)
+        else:
+            cq = norm32_ops.sum_norm(down[:, :Q], self.q_gain, self.eps, out_dtype=x.dtype, want32=False)[1]
         q = ops.linear(cq, self.w_uq)  # [T, H * (d + r)]
         qa = torch.empty((T, H * R), dtype=torch.float32, device=x.device)
         if latent_ops.head_products_supported(q, d + r, self.w_uk_t):

@@ -539,7 +539,7 @@ def test_latent_attention_kernel_sees_exactly_the_window(H, R, r, page, window, 
             assert w.max() < 0.9  # a key outside the window or after the query: nothing stands out
 
 
-def test_latent_store_kernel_turns_halves_with_a_magnitude():
+def test_latent_store_kernel_turns_halves_with_a_magnitude_and_norms_the_query_latent():
     from dispec_b200.ops import latent as LO
     g = torch.Generator().manual_seed(2)
     R, r, page, Q = 20, 8, 4, 3
@@ -552,8 +552,11 @@ def test_latent_store_kernel_turns_halves_with_a_magnitude():
     freq, mag = plain.yarn_table(rot)
     c_pool = torch.full((5, 1, page, R), float("nan"), device="cuda:0")
     r_pool = torch.full((5, 1, page, r), float("nan"), device="cuda:0")
-    LO.latent_store(dev(down), Q, Q + R, dev(gain), 1e-6, dev(freq), 6, pos.cuda(), seq.cuda(), table.cuda(),
-                    c_pool, r_pool, layout="halves", magnitude=mag)
+    q_gain = torch.rand(Q, generator=g) + 0.5
+    cq = LO.latent_store(dev(down), Q, Q + R, dev(gain), 1e-6, dev(freq), 6, pos.cuda(), seq.cuda(), table.cuda(),
+                         c_pool, r_pool, layout="halves", magnitude=mag, query_latent=(0, Q, dev(q_gain), torch.float32))
+    # the query latent's norm comes out of the same launch, for padding rows too
+    assert (cq.cpu().double() - plain.norm_plain(down[:, :Q].double(), q_gain.double(), 1e-6)).abs().max() < 1e-5
     for t in range(6):
         if pos[t] < 0:
             continue

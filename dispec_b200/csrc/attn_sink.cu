@@ -92,11 +92,20 @@ qkv_rotate_store_kernel(const void* __restrict__ qkv, int in_dtype, long ld, con
       st_any(q_out, pool_dtype, (size_t)t * ld_q + idx, turned(row + (size_t)h * Dk, idx % Dk, inv[h], q_norm_w) * q_temp);
     }
   } else {
+    // the widened rows: zeros first (16 bytes a store where the row allows), then every part in its place
     const int wide = maps * Dk;
-    for (int idx = threadIdx.x; idx < H * wide; idx += blockDim.x) {
-      const int h = idx / wide, part = (idx % wide) / Dk;
-      const float v = part == h % maps ? turned(row + (size_t)h * Dk, idx % Dk, inv[h], q_norm_w) * q_temp : 0.f;
-      st_any(q_out, pool_dtype, (size_t)t * ld_q + idx, v);
+    const size_t esz = pool_dtype == DSP_BF16 ? 2 : 4, row_bytes = (size_t)H * wide * esz;
+    char* qrow = reinterpret_cast<char*>(q_out) + (size_t)t * ld_q * esz;
+    if (row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(qrow) % 16 == 0) {
+      for (size_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(qrow)[i] = make_uint4(0, 0, 0, 0);
+    } else {
+      for (int idx = threadIdx.x; idx < H * wide; idx += blockDim.x) st_any(q_out, pool_dtype, (size_t)t * ld_q + idx, 0.f);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < H * Dk; idx += blockDim.x) {
+      const int h = idx / Dk, i = idx % Dk;
+      st_any(q_out, pool_dtype, (size_t)t * ld_q + (size_t)h * wide + (h % maps) * Dk + i,
+             turned(row + (size_t)h * Dk, i, inv[h], q_norm_w) * q_temp);
     }
   }
   if (!write_kv) return;

@@ -67,7 +67,8 @@ __device__ __forceinline__ Best warp_best(Best b) {
   return b;
 }
 
-__global__ void __launch_bounds__(1024)
+// (two blocks of 1,024 threads an SM: 32 registers a thread, so that prompts' blocks of 16 warps fit four an SM)
+__global__ void __launch_bounds__(1024, 2)
 moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float* __restrict__ w, int T, int W, int E,
                  int groups, int keep, int top, int score_kind, int group_kind, int normalize, float weight_scale,
                  int extra, float* __restrict__ extra_out, int* __restrict__ ids, float* __restrict__ wts) {
@@ -188,23 +189,24 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
       if (lane + 32 * k == bi) whole[k] = INT_MIN;
     __syncwarp();
   }
+  // every lane holds each round's winner: the weights' sum is formed in registers (ascending r), the
+  // weights wait in shared memory (the token's row is no longer needed) and go out once, scaled
+  float wsum = 0.f;
   for (int r = 0; r < top; ++r) {
     Best b = {-INFINITY, -1};
     for (int e = lane; e < E; e += 32) b = better(b, Best{sc[e], ok[e] > 0.f ? e : -1});
     b = warp_best(b);
+    const float wr = b.i < 0 ? 0.f : score_kind == 1 ? 1.f / (1.f + expf(-b.v)) : b.v;
+    wsum += wr;
     if (lane == 0) {
       ids[t * top + r] = b.i;
-      wts[t * top + r] = b.i < 0 ? 0.f : score_kind == 1 ? 1.f / (1.f + expf(-b.v)) : b.v;
+      hs[r] = wr;
       if (b.i >= 0) ok[b.i] = 0.f;
     }
     __syncwarp();
   }
-  if (normalize && lane == 0) {
-    float sum = 0.f;
-    for (int r = 0; r < top; ++r) sum += wts[t * top + r];
-    const float f = weight_scale / (sum + 1e-20f);
-    for (int r = 0; r < top; ++r) wts[t * top + r] *= f;
-  }
+  const float f = normalize ? weight_scale / (wsum + 1e-20f) : 1.f;
+  for (int r = lane; r < top; r += 32) wts[t * top + r] = hs[r] * f;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -478,6 +480,7 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
   if (T == 0) return 0;
   DSP_REQUIRE(score_kind == 0 || score_kind == 1, "dsp_moe_route: unknown score kind %d", score_kind);
   DSP_REQUIRE(h && w && ids && wts, "dsp_moe_route: missing operand");
+  DSP_REQUIRE(top <= W, "dsp_moe_route: top=%d exceeds the row's width %d", top, W);
   DSP_REQUIRE(groups <= 32 * GROUPS_PER_LANE, "dsp_moe_route: %d groups are more than the router ranks (%d)", groups,
               32 * GROUPS_PER_LANE);
   DSP_REQUIRE((group_kind == 0 || group_kind == 1) && extra >= 0 && (extra == 0 || extra_out),
@@ -489,7 +492,16 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
   DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts over a width of %d are more than the router kernel holds", E, W);
   // a warp an expert where the block can hold them: the logits are chains of dependent rounds of loads,
   // and a step of a few tokens waits for the longest chain (the sums do not depend on the block's shape)
-  const unsigned threads = 32u * (unsigned)min(max(E + extra, 4), 32);
+  // With many tokens the SMs are full of blocks anyway and what counts is how many fit: warps in a power of
+  // two (17 rows in 17 warps leave room for three blocks an SM, in 16 warps for four).
+  int warps = min(max(E + extra, 4), 32);
+  if (T > 512)
+    for (int w = 32; w >= 4; w >>= 1)
+      if (w <= warps) {
+        warps = w;
+        break;
+      }
+  const unsigned threads = 32u * (unsigned)warps;
   DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)T), dim3(threads), smem, stream, h, h_dtype, ldh, w, T, W, E,
                         groups, keep, top, score_kind, group_kind, normalize, weight_scale, extra, extra_out, ids, wts));
   DSP_CHECK_LAUNCH("dsp_moe_route");

@@ -885,7 +885,7 @@ def milivik_config(shape: str) -> dict:
               "kv_rank": lat["kv_rank"], "q_rank": lat["q_rank"], "scale": (lat["dim"] + lat["rot_dim"]) ** -0.5,
               "mask": {"size": z["window"]},
               "rot": {"base": 1e6, "dims": lat["rot_dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
-    maps = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"] // 2, "vdim": z["vdim"], "diff": 0.3,
+    maps = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"] // 2, "vdim": z["vdim"], "diff": 0.25,
             "scale": (z["dim"] // 2) ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
     period = [{"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": z["ff"]}},
               {"type": "attention", "mixer": maps, "mlp": moe},

@@ -74,15 +74,15 @@ CONFIGS = {
     "wide": dict(config=model(256, 384, [
         latent(8, 64, 32, 64, 128, 192, window=64, rot=32, slowed=(8.0, 128, 32.0, 1.0),
                mlp=moe(16, 4, 128, groups=(4, 2), scale=2.5, shared=256)),
-        diff(8, 2, 64, 128, 0.3, q_temp=(0.5, 64), mlp=dense(512)),
-        latent(18, 32, 16, 32, 64, 64, window=100, rot=16, mlp=moe(8, 2, 64, groups=(2, 1), shared=64)),
+        diff(8, 2, 64, 128, 0.35, q_temp=(0.45, 64), mlp=dense(512)),
+        latent(18, 32, 16, 32, 64, 64, window=100, rot=16, mlp=moe(8, 2, 64, groups=(4, 1), shared=64)),
         diff(4, 1, 16, 32, 0.5, mlp=moe(4, 4, 32)),
-    ], scale=4.0, logit_scale=0.25), seed=43, page_size=32),
+    ], scale=4.0, logit_scale=0.2), seed=43, page_size=32),
     # windows of hundreds of positions (many pages and key tiles; single tokens' keys cut into shares),
     # one of them no multiple of a page, a temperature that first changes far into the sequence
     "long": dict(config=model(128, 200, [
-        latent(4, 16, 32, 32, 64, 64, window=300, rot=32, slowed=(2.0, 256, 32.0, 1.0), mlp=dense(128)),
-        diff(2, 1, 32, 64, 0.3, q_temp=(0.5, 128), mlp=moe(4, 2, 32, groups=(2, 1), scale=1.5, shared=32)),
+        latent(4, 16, 32, 32, 64, 64, window=300, rot=32, slowed=(2.5, 256, 24.0, 1.0), mlp=dense(128)),
+        diff(2, 1, 32, 48, 0.25, q_temp=(0.4, 128), mlp=moe(4, 2, 32, groups=(2, 1), scale=1.5, shared=32)),
         latent(6, 16, 16, 48, 128, 32, window=512, rot=16, mlp=None),
     ]), seed=44, page_size=16),
 }
